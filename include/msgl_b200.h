@@ -1,0 +1,149 @@
+/*
+ * msgl_b200.h — C ABI of the B200 (sm_100a) paged-attention library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * handle (passed as void*, i.e. a cudaStream_t).  No entry point retains a
+ * pointer past the call, synchronises the host with the device, or allocates
+ * device memory: scratch space is supplied by the caller (query its size with
+ * the *_workspace_bytes functions).  Launches are asynchronous on `stream`.
+ *
+ * Each function replaces one operator of the reference extension
+ * `mini_sglang_mlx_kernel` (mini-sglang-mlx-kernel/csrc/bindings.cpp); the
+ * citation beside each declaration names the reference host wrapper whose
+ * argument meaning, validation and error text it keeps.
+ *
+ * Tensors (row-major, innermost stride 1):
+ *   q / out of decode      (batch, num_q_heads, head_dim)
+ *   q / out of prefill     (total_q_tokens, num_q_heads, head_dim)
+ *   k_cache / v_cache      (num_slots, num_kv_heads, head_dim)   one slot = one KV token
+ *   kv_indptr, qo_indptr   (batch + 1) int32, CSR row pointers
+ *   kv_indices             (kv_indptr[batch]) int32, slot id of every KV token
+ *   prefix_lens            (batch) int32, absolute position of a sequence's first query row
+ *   num_kv_splits          (batch) int32, split-KV hint per sequence
+ * Grouped-query mapping: kv_head = q_head / (num_q_heads / num_kv_heads).
+ */
+#ifndef MSGL_B200_H_
+#define MSGL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSGL_ABI_VERSION 1
+
+/* Status codes returned by every int-valued entry point. */
+enum {
+  MSGL_OK = 0,
+  MSGL_BAD_SHAPE = 1,
+  MSGL_BAD_DTYPE = 2,
+  MSGL_UNSUPPORTED_HEAD_DIM = 3,
+  MSGL_BAD_GQA = 4,
+  MSGL_BAD_ARG = 5,
+  MSGL_CUDA_ERROR = 6,
+  MSGL_DEVICE_STATUS = 7 /* a kernel reported a bounded-wait timeout or an out-of-range slot */
+};
+
+/* Element types of q / k_cache / v_cache / out. */
+enum { MSGL_DTYPE_BF16 = 0, MSGL_DTYPE_F16 = 1 };
+
+/* Largest split count the decode workspace layout supports. */
+#define MSGL_MAX_KV_SPLITS 128
+
+int msgl_abi_version(void);
+
+/* Message of the last non-OK status returned on the calling thread ("" if none). */
+const char* msgl_last_error_string(void);
+
+/* Number of SMs of the current device (cached per device); <0 on CUDA error. */
+int msgl_device_sm_count(void);
+
+/*
+ * Bytes of scratch the decode op needs: fp32 partial outputs
+ * (batch, num_q_heads, max_kv_splits, head_dim) followed by fp32 log-sum-exp
+ * (batch, num_q_heads, max_kv_splits).
+ * Replaces the two temporaries of PagedDecodeAttention::eval_gpu
+ * (mini-sglang-mlx-kernel/csrc/paged_decode_attention.cpp:119-131).
+ */
+size_t msgl_decode_workspace_bytes(int batch, int num_q_heads, int head_dim, int max_kv_splits);
+
+/*
+ * Paged decode attention: one query token per sequence over all of its KV
+ * tokens, split-KV partial pass plus log-sum-exp merge pass.
+ * Replaces paged_decode_attention
+ * (mini-sglang-mlx-kernel/csrc/paged_decode_attention.cpp:15-73, binding
+ * csrc/bindings.cpp:36-44) and its two Metal stages
+ * (csrc/paged_decode_attention.metal:313-506, 512-586).
+ * num_kv_splits may be NULL (then every sequence uses max_kv_splits capped by
+ * its length).  Sequences of length 0 produce zeros.
+ */
+int msgl_paged_decode_attention(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* num_kv_splits,
+    void* out, void* workspace, size_t workspace_bytes,
+    int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t num_slots,
+    int dtype, float sm_scale, int max_kv_splits, void* stream);
+
+/*
+ * Bytes of scratch the prefill op needs for the given problem (split-KV
+ * partials when there are too few query tiles to fill the GPU, plus a small
+ * planning area).  total_kv = kv_indptr[batch] = length of kv_indices.
+ * No counterpart in the reference (its prefill kernel never splits KV).
+ */
+size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, int num_q_heads,
+                                    int num_kv_heads, int head_dim, int max_len_extend,
+                                    int sliding_window_size);
+
+/*
+ * Paged prefill / extend attention over prefix + new tokens with the four
+ * mask modes (causal, full, causal+window, bidirectional+window); also the
+ * speculative-verify and draft-block shapes.
+ * Replaces paged_prefill_attention
+ * (mini-sglang-mlx-kernel/csrc/paged_prefill_attention.cpp:18-87, binding
+ * csrc/bindings.cpp:45-55) and its Metal kernel
+ * (csrc/paged_prefill_attention.metal:382-640).
+ * Key t of a sequence is visible to query row p iff t < kv_len and
+ * (is_cross_attention or t <= prefix_len + p) and
+ * (sliding_window_size == 0 or t >= prefix_len + p - sliding_window_size + 1).
+ * Rows with no visible key produce zeros.
+ */
+int msgl_paged_prefill_attention(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* qo_indptr, const int32_t* kv_indptr, const int32_t* kv_indices,
+    const int32_t* prefix_lens, void* out, void* workspace, size_t workspace_bytes,
+    int batch, int total_q, int64_t total_kv, int num_q_heads, int num_kv_heads, int head_dim,
+    int64_t num_slots, int dtype, float sm_scale, int max_len_extend,
+    int is_cross_attention, int sliding_window_size, void* stream);
+
+/*
+ * Scatter new keys/values into the pool: k_cache[indices[r]] = k[r],
+ * v_cache[indices[r]] = v[r] for r < length.  Row strides are in elements.
+ * Replaces store_kv_cache
+ * (mini-sglang-mlx-kernel/csrc/store_kv_cache.cpp:13-107, kernel
+ * csrc/store_kv_cache.metal:7-31).
+ */
+int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, const void* k,
+                        const void* v, int length, int num_kv_heads, int head_dim,
+                        int64_t num_slots, int64_t cache_row_stride, int64_t input_row_stride,
+                        int dtype, void* stream);
+
+/*
+ * CSR metadata from a page table: for sequence b, copies
+ * page_table[table_idx[b], 0:kv_lens[b]] to kv_indices[kv_indptr[b]:...]
+ * in one launch.  kv_indptr (batch+1) must already hold the exclusive prefix
+ * sum of kv_lens.
+ * Replaces the per-request slice-and-concatenate loops of
+ * AttnBackend.build_prefill_metadata / build_decode_metadata
+ * (mini_sglang_mlx/attention/backend.py:239-244, 279-284).
+ */
+int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
+                           const int32_t* table_idx, const int32_t* kv_indptr,
+                           int32_t* kv_indices, int batch, int64_t total_kv, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MSGL_B200_H_ */

@@ -1,0 +1,189 @@
+"""Attention backend: CSR metadata from the page table, K/V store, dispatch.
+
+Mirror of the reference's ``AttnBackend``
+(mini_sglang_mlx/attention/backend.py:64-307): same class, method and field
+names and the same meaning of every argument, over CUDA ``torch.Tensor``.
+Differences, all inside the boundary:
+
+* ``kv_indices`` is gathered from the device-resident page table by one kernel
+  launch instead of a per-request slice-and-concatenate loop on the host
+  (reference lines 239-244 and 279-284); only the (batch+1)-sized pointer
+  arrays are built on the host and copied.
+* ``num_kv_splits`` is chosen for a 148-SM part from the batch's total work
+  (``compute_num_kv_splits``); ``policy="reference"`` keeps the reference rule
+  ``min(32, max(1, ceil(L/128)))`` (lines 304-307).  The result of the decode
+  op does not depend on the choice beyond fp32 rounding.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _lib
+from ..kernel import gather_kv_indices, paged_decode_attention, paged_prefill_attention
+
+MAX_KV_SPLITS = 32
+
+
+@dataclass
+class BaseAttnMetadata:
+    positions: torch.Tensor
+
+    def get_last_indices(self, bs: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
+@dataclass
+class PrefillMetadata(BaseAttnMetadata):
+    qo_indptr: torch.Tensor     # (batch + 1,) int32
+    kv_indptr: torch.Tensor     # (batch + 1,) int32
+    kv_indices: torch.Tensor    # (total_kv,) int32 slot ids
+    prefix_lens: torch.Tensor   # (batch,) int32
+    max_len_extend: int
+
+    def get_last_indices(self, bs: int) -> torch.Tensor:
+        return self.qo_indptr[1:1 + bs] - 1
+
+
+@dataclass
+class DecodeMetadata(BaseAttnMetadata):
+    kv_indptr: torch.Tensor     # (batch + 1,) int32
+    kv_indices: torch.Tensor    # (total_kv,) int32 slot ids
+    num_kv_splits: torch.Tensor  # (batch,) int32
+    max_kv_splits: int
+
+    def get_last_indices(self, bs: int) -> torch.Tensor:
+        return torch.arange(bs, dtype=torch.int32, device=self.kv_indptr.device)
+
+
+AttnMetadata = PrefillMetadata | DecodeMetadata
+
+
+def compute_num_kv_splits(kv_lens: Sequence[int], num_kv_heads: int, *, sm_count: int = 148,
+                          max_kv_splits: int = MAX_KV_SPLITS, policy: str = "b200") -> List[int]:
+    """Per-sequence split count of the decode op.
+
+    ``reference``: ``min(max, max(1, ceil(L/128)))`` (reference lines 304-307).
+    ``b200``: one split per ``chunk`` tokens where ``chunk`` spreads the batch's
+    ``sum(L) * num_kv_heads`` token-heads over about 16 CTAs per SM, clamped to
+    [256, 4096] tokens: enough CTAs to fill the SMs at small batch, small
+    enough CTAs that a long sequence does not leave a tail.
+    """
+    if policy == "reference":
+        return [min(max_kv_splits, max(1, (l + 127) // 128)) for l in kv_lens]
+    total = sum(kv_lens) * num_kv_heads
+    chunk = -(-total // (sm_count * 16))
+    chunk = min(4096, max(256, chunk))
+    chunk = -(-chunk // 64) * 64
+    return [min(max_kv_splits, max(1, -(-l // chunk))) for l in kv_lens]
+
+
+def _build_indptr(lens: Sequence[int], device) -> torch.Tensor:
+    cs = [0]
+    for l in lens:
+        cs.append(cs[-1] + int(l))
+    return torch.tensor(cs, dtype=torch.int32).to(device, non_blocking=True)
+
+
+class AttnBackend:
+    """Paged attention backend for B200 using the msgl C-ABI operators."""
+
+    def __init__(self, config, kvcache, page_table: torch.Tensor, *,
+                 split_policy: str = "b200") -> None:
+        self.config = config
+        self.kvcache = kvcache
+        self.page_table = page_table      # (rows, max_seq_len) int32 per-token slot ids, on device
+        self.sm_scale = 1.0 / math.sqrt(config.head_dim)
+        self.split_policy = split_policy
+        self._sm_count: Optional[int] = None
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layer_id: int, batch, *,
+                is_cross_attention: bool = False, sliding_window_size: int = 0) -> torch.Tensor:
+        """Write this step's K/V rows at ``batch.out_loc`` and run paged attention.
+
+        q ``[N, Hq, D]``, k/v ``[N, Hkv, D]``.  The mask flags compose as in the
+        reference (lines 97-132): causal / full / causal+window /
+        bidirectional+window; the decode path accepts neither.
+        """
+        assert sliding_window_size >= 0, (
+            f"sliding_window_size must be >= 0, got {sliding_window_size}")
+        metadata = batch.attn_metadata
+        self.kvcache.store_kv(k, v, batch.out_loc, layer_id)
+        k_cache = self.kvcache.k_cache(layer_id)
+        v_cache = self.kvcache.v_cache(layer_id)
+        if isinstance(metadata, PrefillMetadata):
+            return paged_prefill_attention(
+                q, k_cache, v_cache, metadata.qo_indptr, metadata.kv_indptr, metadata.kv_indices,
+                metadata.prefix_lens, sm_scale=self.sm_scale, max_len_extend=metadata.max_len_extend,
+                is_cross_attention=is_cross_attention, sliding_window_size=sliding_window_size)
+        assert isinstance(metadata, DecodeMetadata)
+        assert not is_cross_attention and sliding_window_size == 0, (
+            "is_cross_attention / sliding_window_size are only supported on the prefill path.")
+        return paged_decode_attention(
+            q, k_cache, v_cache, metadata.kv_indptr, metadata.kv_indices, metadata.num_kv_splits,
+            sm_scale=self.sm_scale, max_kv_splits=metadata.max_kv_splits)
+
+    def store_kv_only(self, k: torch.Tensor, v: torch.Tensor, out_loc: torch.Tensor,
+                      layer_id: int) -> None:
+        """Write K/V into the pool without running attention (reference lines 174-196)."""
+        self.kvcache.store_kv(k, v, out_loc, layer_id)
+
+    # ------------------------------------------------------------------ metadata
+    def prepare_metadata(self, batch) -> None:
+        reqs = batch.padded_reqs
+        if batch.is_prefill:
+            batch.attn_metadata = self.build_prefill_metadata(reqs)
+        else:
+            batch.attn_metadata = self.build_decode_metadata(reqs)
+
+    def _kv_indices(self, reqs, kv_lens: Sequence[int], kv_indptr: torch.Tensor) -> torch.Tensor:
+        table_idx = torch.tensor([r.table_idx for r in reqs], dtype=torch.int32).to(
+            self.page_table.device, non_blocking=True)
+        return gather_kv_indices(self.page_table, table_idx, kv_indptr, sum(kv_lens))
+
+    def build_prefill_metadata(self, reqs, *, extend_lens: Optional[List[int]] = None,
+                               kv_lens: Optional[List[int]] = None,
+                               positions: Optional[torch.Tensor] = None) -> PrefillMetadata:
+        """Reference lines 205-254; ``extend_lens`` / ``kv_lens`` overrides serve a
+        virtual extend window such as a K+1-token verify."""
+        dev = self.page_table.device
+        if extend_lens is None:
+            extend_lens = [req.extend_len for req in reqs]
+        if kv_lens is None:
+            kv_lens = [req.device_len for req in reqs]
+        cached_lens = [kv_lens[i] - extend_lens[i] for i in range(len(reqs))]
+        if positions is None:
+            positions = torch.cat(
+                [torch.arange(cached_lens[i], kv_lens[i], dtype=torch.int32)
+                 for i in range(len(reqs))]).to(dev, non_blocking=True)
+        qo_indptr = _build_indptr(extend_lens, dev)
+        kv_indptr = _build_indptr(kv_lens, dev)
+        kv_indices = self._kv_indices(reqs, kv_lens, kv_indptr)
+        prefix_lens = torch.tensor(cached_lens, dtype=torch.int32).to(dev, non_blocking=True)
+        return PrefillMetadata(positions=positions, qo_indptr=qo_indptr, kv_indptr=kv_indptr,
+                               kv_indices=kv_indices, prefix_lens=prefix_lens,
+                               max_len_extend=max(extend_lens))
+
+    def build_decode_metadata(self, reqs, *, kv_lens: Optional[List[int]] = None,
+                              positions: Optional[torch.Tensor] = None) -> DecodeMetadata:
+        """Reference lines 256-293."""
+        dev = self.page_table.device
+        if kv_lens is None:
+            kv_lens = [req.device_len for req in reqs]
+        if positions is None:
+            positions = torch.tensor([req.cached_len for req in reqs], dtype=torch.int32).to(
+                dev, non_blocking=True)
+        kv_indptr = _build_indptr(kv_lens, dev)
+        kv_indices = self._kv_indices(reqs, kv_lens, kv_indptr)
+        if self._sm_count is None:
+            with torch.cuda.device(dev):
+                self._sm_count = max(1, _lib.lib().msgl_device_sm_count())
+        splits = compute_num_kv_splits(kv_lens, self.config.num_kv_heads, sm_count=self._sm_count,
+                                       max_kv_splits=MAX_KV_SPLITS, policy=self.split_policy)
+        num_kv_splits = torch.tensor(splits, dtype=torch.int32).to(dev, non_blocking=True)
+        return DecodeMetadata(positions=positions, kv_indptr=kv_indptr, kv_indices=kv_indices,
+                              num_kv_splits=num_kv_splits, max_kv_splits=MAX_KV_SPLITS)

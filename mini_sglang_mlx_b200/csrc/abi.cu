@@ -1,0 +1,388 @@
+// C-ABI entry points of the B200 paged-attention library: argument
+// validation (same rules and message prefixes as the reference host wrappers),
+// scratch layout, launch configuration.  Declarations: include/msgl_b200.h.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/msgl_b200.h"
+#include "decode_splitkv.cuh"
+#include "prefill_mma.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+int cuda_fail(const char* op, cudaError_t e) {
+  return fail(MSGL_CUDA_ERROR, std::string(op) + ": CUDA error: " + cudaGetErrorString(e));
+}
+
+constexpr size_t kStatusBytes = 256;  // head of every workspace: device status word
+
+constexpr int kDecWarps = 4;
+constexpr int kDecStages = 3;
+constexpr int kDecCtaTokens = kDecWarps * msgl::kDecodeGroupTokens;
+
+int sm_count_cached() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached_sms = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (dev != cached_dev) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    cached_dev = dev;
+    cached_sms = sms;
+  }
+  return cached_sms;
+}
+
+template <typename K>
+cudaError_t allow_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+// ---- prefill scheduling decision (shared by the workspace query and the launch)
+struct PrefillPlan {
+  int kv_chunk;        // 0 = no kv split
+  int64_t items;       // grid.x
+  size_t part_o_bytes, part_ml_bytes, plan_bytes;
+};
+
+PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int hkv, int head_dim,
+                         int max_len_extend, int window, int sms) {
+  PrefillPlan pl{};
+  const int G = hq / hkv;
+  const int BM = msgl::kMmaBM;
+  const int64_t qtiles = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, 0);
+  int64_t visible = total_kv;
+  if (window > 0) {
+    const int64_t w = static_cast<int64_t>(batch) * (static_cast<int64_t>(window) + max_len_extend);
+    if (w < visible) visible = w;
+  }
+  pl.kv_chunk = 0;
+  if (qtiles * hkv < 2LL * sms && visible > 0) {
+    const int64_t nqt_max = (static_cast<int64_t>(max_len_extend) * G + BM - 1) / BM;
+    int64_t chunk = visible * nqt_max * hkv / (4LL * sms);
+    if (chunk < 256) chunk = 256;
+    chunk = (chunk + 63) / 64 * 64;
+    if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
+  }
+  pl.items = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, pl.kv_chunk);
+  if (pl.kv_chunk > 0) {
+    const size_t slots = static_cast<size_t>(pl.items) * hkv;
+    pl.part_o_bytes = slots * BM * head_dim * sizeof(float);
+    pl.part_ml_bytes = slots * BM * 2 * sizeof(float);
+    pl.plan_bytes = (static_cast<size_t>(batch) * 2 * sizeof(int) + 255) / 256 * 256;
+  }
+  return pl;
+}
+
+// ---- small data-movement kernels
+template <int VEC_BYTES>
+__global__ void store_kv_kernel(unsigned char* __restrict__ kc, unsigned char* __restrict__ vc,
+                                const int32_t* __restrict__ indices,
+                                const unsigned char* __restrict__ k,
+                                const unsigned char* __restrict__ v, int length, int vec_per_row,
+                                int64_t cache_row_bytes, int64_t input_row_bytes,
+                                int64_t num_slots, int* status) {
+  using V = typename std::conditional<VEC_BYTES == 16, uint4, uint2>::type;
+  const int64_t total = static_cast<int64_t>(length) * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / vec_per_row);
+    const int c = static_cast<int>(i - static_cast<int64_t>(r) * vec_per_row);
+    const int slot = indices[r];
+    if (slot < 0 || slot >= num_slots) {
+      if (status) atomicExch(status, 2);
+      continue;
+    }
+    const int64_t src = r * input_row_bytes + static_cast<int64_t>(c) * VEC_BYTES;
+    const int64_t dst = slot * cache_row_bytes + static_cast<int64_t>(c) * VEC_BYTES;
+    *reinterpret_cast<V*>(kc + dst) = *reinterpret_cast<const V*>(k + src);
+    *reinterpret_cast<V*>(vc + dst) = *reinterpret_cast<const V*>(v + src);
+  }
+}
+
+__global__ void gather_kv_indices_kernel(const int32_t* __restrict__ page_table,
+                                         int64_t row_stride, const int32_t* __restrict__ table_idx,
+                                         const int32_t* __restrict__ kv_indptr,
+                                         int32_t* __restrict__ kv_indices, int batch) {
+  const int b = blockIdx.y;
+  const int begin = kv_indptr[b];
+  const int len = kv_indptr[b + 1] - begin;
+  const int32_t* row = page_table + static_cast<int64_t>(table_idx[b]) * row_stride;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < len; t += gridDim.x * blockDim.x)
+    kv_indices[begin + t] = row[t];
+}
+
+template <typename T>
+int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s) {
+  dim3 grid1(p.max_splits, p.hkv, p.batch);
+  dim3 grid2(p.hq, p.batch);
+  if (head_dim == 128) {
+    auto k1 = msgl::decode_partial_kernel<T, 128, kDecWarps, kDecStages>;
+    constexpr int smem = kDecWarps * kDecStages * 2 * msgl::kDecodeGroupTokens * 256;
+    cudaError_t e = allow_smem(k1, smem);
+    if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
+    k1<<<grid1, kDecWarps * 32, smem, s>>>(p);
+    msgl::decode_merge_kernel<T, 128, kDecCtaTokens><<<grid2, 128, 0, s>>>(p);
+  } else {
+    return fail(MSGL_UNSUPPORTED_HEAD_DIM,
+                "paged_decode_attention: head_dim 256 is not built in this library");
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
+  return MSGL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int msgl_abi_version(void) { return MSGL_ABI_VERSION; }
+
+const char* msgl_last_error_string(void) { return g_last_error.c_str(); }
+
+int msgl_device_sm_count(void) { return sm_count_cached(); }
+
+size_t msgl_decode_workspace_bytes(int batch, int num_q_heads, int head_dim, int max_kv_splits) {
+  if (batch <= 0 || num_q_heads <= 0 || head_dim <= 0 || max_kv_splits <= 0) return kStatusBytes;
+  const size_t rows = static_cast<size_t>(batch) * num_q_heads * max_kv_splits;
+  return kStatusBytes + rows * head_dim * sizeof(float) + rows * sizeof(float);
+}
+
+int msgl_paged_decode_attention(const void* q, const void* k_cache, const void* v_cache,
+                                const int32_t* kv_indptr, const int32_t* kv_indices,
+                                const int32_t* num_kv_splits, void* out, void* workspace,
+                                size_t workspace_bytes, int batch, int num_q_heads,
+                                int num_kv_heads, int head_dim, int64_t num_slots, int dtype,
+                                float sm_scale, int max_kv_splits, void* stream) {
+  const char* op = "paged_decode_attention: ";
+  if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "q must be 3D (batch, num_q_heads, head_dim)");
+  if (head_dim != 128 && head_dim != 256)
+    return fail(MSGL_UNSUPPORTED_HEAD_DIM, std::string(op) + "head_dim must be 128 or 256");
+  if (num_q_heads % num_kv_heads != 0)
+    return fail(MSGL_BAD_GQA, std::string(op) + "num_q_heads must be a multiple of num_kv_heads");
+  if (num_q_heads / num_kv_heads > 16)
+    return fail(MSGL_BAD_GQA, std::string(op) + "only q_heads/kv_heads <= 16 is supported");
+  if (dtype != MSGL_DTYPE_BF16 && dtype != MSGL_DTYPE_F16)
+    return fail(MSGL_BAD_DTYPE, std::string(op) + "unsupported dtype, must be float16 or bfloat16");
+  if (max_kv_splits < 1 || max_kv_splits > MSGL_MAX_KV_SPLITS)
+    return fail(MSGL_BAD_ARG, std::string(op) + "max_kv_splits must be in [1, 128]");
+  if (batch == 0) return MSGL_OK;
+  if (batch > 65535 || num_kv_heads > 65535)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "batch and num_kv_heads must be <= 65535");
+  if (!q || !k_cache || !v_cache || !kv_indptr || !kv_indices || !out)
+    return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  const size_t need = msgl_decode_workspace_bytes(batch, num_q_heads, head_dim, max_kv_splits);
+  if (!workspace || workspace_bytes < need)
+    return fail(MSGL_BAD_ARG, std::string(op) + "workspace too small");
+
+  msgl::DecodeParams p{};
+  p.q = q;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.kv_indptr = kv_indptr;
+  p.kv_indices = kv_indices;
+  p.num_kv_splits = num_kv_splits;
+  p.out = out;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.part_o = reinterpret_cast<float*>(ws + kStatusBytes);
+  p.part_lse = p.part_o + static_cast<size_t>(batch) * num_q_heads * max_kv_splits * head_dim;
+  p.batch = batch;
+  p.hq = num_q_heads;
+  p.hkv = num_kv_heads;
+  p.group = num_q_heads / num_kv_heads;
+  p.max_splits = max_kv_splits;
+  p.num_slots = num_slots;
+  p.scale_log2 = sm_scale * msgl::kLog2e;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == MSGL_DTYPE_BF16) return launch_decode<__nv_bfloat16>(p, head_dim, s);
+  return launch_decode<__half>(p, head_dim, s);
+}
+
+size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, int num_q_heads,
+                                    int num_kv_heads, int head_dim, int max_len_extend,
+                                    int sliding_window_size) {
+  if (batch <= 0 || total_q <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 ||
+      num_q_heads % num_kv_heads != 0)
+    return kStatusBytes;
+  const int sms = sm_count_cached();
+  const PrefillPlan pl = plan_prefill(batch, total_q, total_kv, num_q_heads, num_kv_heads,
+                                      head_dim, max_len_extend, sliding_window_size,
+                                      sms > 0 ? sms : 148);
+  return kStatusBytes + pl.plan_bytes + pl.part_ml_bytes + pl.part_o_bytes;
+}
+
+int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
+                                 const int32_t* qo_indptr, const int32_t* kv_indptr,
+                                 const int32_t* kv_indices, const int32_t* prefix_lens, void* out,
+                                 void* workspace, size_t workspace_bytes, int batch, int total_q,
+                                 int64_t total_kv, int num_q_heads, int num_kv_heads,
+                                 int head_dim, int64_t num_slots, int dtype, float sm_scale,
+                                 int max_len_extend, int is_cross_attention,
+                                 int sliding_window_size, void* stream) {
+  const char* op = "paged_prefill_attention: ";
+  if (total_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0 || total_kv < 0)
+    return fail(MSGL_BAD_SHAPE,
+                std::string(op) + "q must be 3D (total_q_tokens, num_q_heads, head_dim)");
+  if (head_dim != 128 && head_dim != 256)
+    return fail(MSGL_UNSUPPORTED_HEAD_DIM, std::string(op) + "head_dim must be 128 or 256");
+  if (num_q_heads % num_kv_heads != 0)
+    return fail(MSGL_BAD_GQA, std::string(op) + "num_q_heads must be a multiple of num_kv_heads");
+  if (sliding_window_size < 0)
+    return fail(MSGL_BAD_ARG, std::string(op) + "sliding_window_size must be >= 0");
+  if (batch <= 0) return fail(MSGL_BAD_SHAPE, std::string(op) + "batch must be > 0");
+  if (dtype != MSGL_DTYPE_BF16 && dtype != MSGL_DTYPE_F16)
+    return fail(MSGL_BAD_DTYPE, std::string(op) + "unsupported dtype, must be float16 or bfloat16");
+  if (head_dim != 128)
+    return fail(MSGL_UNSUPPORTED_HEAD_DIM,
+                std::string(op) + "head_dim 256 is not built in this library");
+  if (total_q == 0) return MSGL_OK;
+  if (num_kv_heads > 65535)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "num_kv_heads must be <= 65535");
+  if (max_len_extend < 1) max_len_extend = 1;
+  if (!q || !k_cache || !v_cache || !qo_indptr || !kv_indptr || !kv_indices || !prefix_lens || !out)
+    return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  const int sms = sm_count_cached();
+  if (sms <= 0) return fail(MSGL_CUDA_ERROR, std::string(op) + "cannot query the device");
+  const PrefillPlan pl = plan_prefill(batch, total_q, total_kv, num_q_heads, num_kv_heads,
+                                      head_dim, max_len_extend, sliding_window_size, sms);
+  const size_t need = kStatusBytes + pl.plan_bytes + pl.part_ml_bytes + pl.part_o_bytes;
+  if (!workspace || workspace_bytes < need)
+    return fail(MSGL_BAD_ARG, std::string(op) + "workspace too small");
+  if (pl.items > 0x7fffffffLL || num_q_heads > 65535)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "problem too large for one launch");
+
+  msgl::PrefillParams p{};
+  p.q = q;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.qo_indptr = qo_indptr;
+  p.kv_indptr = kv_indptr;
+  p.kv_indices = kv_indices;
+  p.prefix_lens = prefix_lens;
+  p.out = out;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  if (pl.kv_chunk > 0) {
+    p.plan = reinterpret_cast<int*>(ws + kStatusBytes);
+    p.part_ml = reinterpret_cast<float*>(ws + kStatusBytes + pl.plan_bytes);
+    p.part_o = reinterpret_cast<float*>(ws + kStatusBytes + pl.plan_bytes + pl.part_ml_bytes);
+  }
+  p.batch = batch;
+  p.total_q = total_q;
+  p.hq = num_q_heads;
+  p.hkv = num_kv_heads;
+  p.group = num_q_heads / num_kv_heads;
+  p.num_slots = num_slots;
+  p.scale_log2 = sm_scale * msgl::kLog2e;
+  p.is_cross = is_cross_attention ? 1 : 0;
+  p.window = sliding_window_size;
+  p.kv_chunk = pl.kv_chunk;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  constexpr int smem = msgl::kMmaStages * 2 * msgl::kMmaBN * 256;
+  dim3 grid(static_cast<unsigned>(pl.items), num_kv_heads);
+  dim3 mgrid(total_q, num_q_heads);
+  cudaError_t e;
+  if (dtype == MSGL_DTYPE_BF16) {
+    auto k = msgl::prefill_mma_kernel<__nv_bfloat16, 128>;
+    if ((e = allow_smem(k, smem)) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
+    k<<<grid, msgl::kMmaWarps * 32, smem, s>>>(p);
+    if (pl.kv_chunk > 0)
+      msgl::prefill_merge_kernel<__nv_bfloat16, 128, msgl::kMmaBM><<<mgrid, 128, 0, s>>>(p);
+  } else {
+    auto k = msgl::prefill_mma_kernel<__half, 128>;
+    if ((e = allow_smem(k, smem)) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
+    k<<<grid, msgl::kMmaWarps * 32, smem, s>>>(p);
+    if (pl.kv_chunk > 0)
+      msgl::prefill_merge_kernel<__half, 128, msgl::kMmaBM><<<mgrid, 128, 0, s>>>(p);
+  }
+  if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
+  return MSGL_OK;
+}
+
+int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, const void* k,
+                        const void* v, int length, int num_kv_heads, int head_dim,
+                        int64_t num_slots, int64_t cache_row_stride, int64_t input_row_stride,
+                        int dtype, void* stream) {
+  const char* op = "store_kv_cache: ";
+  if (length < 0 || num_kv_heads <= 0 || head_dim <= 0 || num_slots < 0)
+    return fail(MSGL_BAD_SHAPE,
+                std::string(op) + "k and v shape must be (length, num_kv_heads, head_dim)");
+  if (head_dim % 4 != 0)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "head_dim must be a multiple of 4");
+  if (dtype != MSGL_DTYPE_BF16 && dtype != MSGL_DTYPE_F16)
+    return fail(MSGL_BAD_DTYPE, std::string(op) + "k_cache, v_cache, k, v must have the same dtype");
+  const int64_t row_elems = static_cast<int64_t>(num_kv_heads) * head_dim;
+  if (cache_row_stride < row_elems || input_row_stride < row_elems)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "row stride smaller than num_kv_heads*head_dim");
+  if (length == 0) return MSGL_OK;
+  if (!k_cache || !v_cache || !indices || !k || !v)
+    return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  const int64_t row_bytes = row_elems * 2;
+  const int64_t crb = cache_row_stride * 2, irb = input_row_stride * 2;
+  auto aligned = [](const void* ptr, int64_t a) { return reinterpret_cast<uintptr_t>(ptr) % a == 0; };
+  const bool vec16 = row_bytes % 16 == 0 && crb % 16 == 0 && irb % 16 == 0 && aligned(k_cache, 16) &&
+                     aligned(v_cache, 16) && aligned(k, 16) && aligned(v, 16);
+  const bool vec8 = crb % 8 == 0 && irb % 8 == 0 && aligned(k_cache, 8) && aligned(v_cache, 8) &&
+                    aligned(k, 8) && aligned(v, 8);
+  if (!vec16 && !vec8)
+    return fail(MSGL_BAD_ARG, std::string(op) + "tensors must be 8-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int vec = vec16 ? 16 : 8;
+  const int vec_per_row = static_cast<int>(row_bytes / vec);
+  const int64_t total = static_cast<int64_t>(length) * vec_per_row;
+  const int threads = 256;
+  int sms = sm_count_cached();
+  if (sms <= 0) sms = 148;
+  int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > static_cast<int64_t>(sms) * 16) blocks = static_cast<int64_t>(sms) * 16;
+  if (vec16)
+    store_kv_kernel<16><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+        static_cast<unsigned char*>(k_cache), static_cast<unsigned char*>(v_cache), indices,
+        static_cast<const unsigned char*>(k), static_cast<const unsigned char*>(v), length,
+        vec_per_row, crb, irb, num_slots, nullptr);
+  else
+    store_kv_kernel<8><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+        static_cast<unsigned char*>(k_cache), static_cast<unsigned char*>(v_cache), indices,
+        static_cast<const unsigned char*>(k), static_cast<const unsigned char*>(v), length,
+        vec_per_row, crb, irb, num_slots, nullptr);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("store_kv_cache", e);
+  return MSGL_OK;
+}
+
+int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
+                           const int32_t* table_idx, const int32_t* kv_indptr,
+                           int32_t* kv_indices, int batch, int64_t total_kv, void* stream) {
+  const char* op = "gather_kv_indices: ";
+  if (batch < 0 || total_kv < 0 || table_row_stride < 0)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "negative size");
+  if (batch == 0 || total_kv == 0) return MSGL_OK;
+  if (batch > 65535) return fail(MSGL_BAD_SHAPE, std::string(op) + "batch must be <= 65535");
+  if (!page_table || !table_idx || !kv_indptr || !kv_indices)
+    return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  const int64_t avg = total_kv / batch + 1;
+  int bx = static_cast<int>((avg + 255) / 256);
+  if (bx > 64) bx = 64;
+  dim3 grid(bx, batch);
+  gather_kv_indices_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      page_table, table_row_stride, table_idx, kv_indptr, kv_indices, batch);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("gather_kv_indices", e);
+  return MSGL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,214 @@
+"""Operators of the reference extension ``mini_sglang_mlx_kernel`` on B200.
+
+Same names, argument order and keyword arguments as the reference bindings
+(mini-sglang-mlx-kernel/csrc/bindings.cpp:27-55), with ``mx.array`` replaced by
+CUDA ``torch.Tensor``.  Each call validates what only the tensor objects can
+tell (rank, dtype, device, contiguity), hands raw pointers to the C-ABI
+library on the current (or given) CUDA stream and returns without a host
+synchronisation.  Errors surface as ``RuntimeError`` with the reference's
+op-prefixed messages.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+__all__ = [
+    "paged_decode_attention",
+    "paged_prefill_attention",
+    "store_kv_cache",
+    "gather_kv_indices",
+    "device_status",
+]
+
+_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
+
+# scratch per (device index, stream handle); grown on demand, never shrunk
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _stream_handle(stream, device: torch.device) -> int:
+    if stream is None:
+        return torch.cuda.current_stream(device).cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    return int(stream)
+
+
+def _workspace(nbytes: int, device: torch.device, stream_handle: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_handle)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        # zero-filled so that the device status word at its head starts clear
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def device_status(device=None) -> int:
+    """Synchronise and return the OR of the device status words of every
+    workspace on ``device`` (0 = no kernel reported an out-of-range slot),
+    clearing them."""
+    torch.cuda.synchronize(device)
+    status = 0
+    for ws in _workspaces.values():
+        word = ws[:4].view(torch.int32)
+        status |= int(word.item())
+        word.zero_()
+    return status
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_common(op: str, q, k_cache, v_cache, index_arrays, index_msg: str, q_msg: str):
+    _require(q.dim() == 3, f"{op}: {q_msg}")
+    _require(k_cache.dim() == 3 and v_cache.dim() == 3,
+             f"{op}: k_cache and v_cache must be 3D (num_pages, num_kv_heads, head_dim)")
+    _require(all(a.dim() == 1 for a in index_arrays), f"{op}: {index_msg}")
+    _require(q.is_cuda, f"{op}: tensors must live on a CUDA device")
+    for t in (k_cache, v_cache, *index_arrays):
+        _require(t.device == q.device, f"{op}: all tensors must be on the same device")
+    _require(q.dtype in _DTYPES, f"{op}: unsupported dtype, must be float16 or bfloat16")
+    _require(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype,
+             f"{op}: q, k_cache and v_cache must have the same dtype")
+    for a in index_arrays:
+        _require(a.dtype == torch.int32, f"{op}: index arrays must be int32")
+        _require(a.is_contiguous(), f"{op}: index arrays must be contiguous")
+    _require(q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(),
+             f"{op}: q, k_cache and v_cache must be contiguous")
+    _require(k_cache.shape == v_cache.shape, f"{op}: v_cache shape must match k_cache")
+
+
+def paged_decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits,
+                           sm_scale: float, max_kv_splits: int, *, stream=None) -> torch.Tensor:
+    """Decode attention of one query token per sequence over its paged KV.
+
+    q ``(batch, Hq, D)``; caches ``(num_slots, Hkv, D)``; ``kv_indptr``
+    ``(batch+1)``, ``kv_indices`` ``(total_kv)``, ``num_kv_splits`` ``(batch)``
+    int32.  Returns ``(batch, Hq, D)`` in q's dtype.  Signature of the
+    reference op: mini-sglang-mlx-kernel/csrc/bindings.cpp:36-44.
+    """
+    op = "paged_decode_attention"
+    _check_common(op, q, k_cache, v_cache, (kv_indptr, kv_indices, num_kv_splits),
+                  "kv_indptr, kv_indices, num_kv_splits must be 1D",
+                  "q must be 3D (batch, num_q_heads, head_dim)")
+    batch, hq, d = q.shape
+    _require(k_cache.shape[2] == d, f"{op}: cache head_dim must match q head_dim")
+    _require(kv_indptr.numel() == batch + 1 and num_kv_splits.numel() == batch,
+             f"{op}: kv_indptr must have batch+1 and num_kv_splits batch entries")
+    out = torch.empty_like(q)
+    sh = _stream_handle(stream, q.device)
+    lib = _lib.lib()
+    with torch.cuda.device(q.device):
+        need = lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits))
+        ws = _workspace(need, q.device, sh)
+        _lib.check(lib.msgl_paged_decode_attention(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kv_indptr.data_ptr(),
+            kv_indices.data_ptr(), num_kv_splits.data_ptr(), out.data_ptr(), ws.data_ptr(),
+            ws.numel(), batch, hq, k_cache.shape[1], d, k_cache.shape[0], _DTYPES[q.dtype],
+            float(sm_scale), int(max_kv_splits), sh))
+    return out
+
+
+def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens,
+                            sm_scale: float, max_len_extend: int, *,
+                            is_cross_attention: bool = False, sliding_window_size: int = 0,
+                            stream=None) -> torch.Tensor:
+    """Ragged multi-token attention over prefix + extend tokens of paged KV.
+
+    q ``(total_q, Hq, D)``; ``qo_indptr``/``kv_indptr`` ``(batch+1)``,
+    ``kv_indices`` ``(total_kv)``, ``prefix_lens`` ``(batch)`` int32.  Mask:
+    causal by default; ``is_cross_attention`` drops the causal bound;
+    ``sliding_window_size`` W > 0 keeps keys at positions >= pos - W + 1.
+    Signature of the reference op: mini-sglang-mlx-kernel/csrc/bindings.cpp:45-55.
+    """
+    op = "paged_prefill_attention"
+    _check_common(op, q, k_cache, v_cache, (qo_indptr, kv_indptr, kv_indices, prefix_lens),
+                  "qo_indptr, kv_indptr, kv_indices, prefix_lens must be 1D",
+                  "q must be 3D (total_q_tokens, num_q_heads, head_dim)")
+    total_q, hq, d = q.shape
+    _require(k_cache.shape[2] == d, f"{op}: cache head_dim must match q head_dim")
+    batch = qo_indptr.numel() - 1
+    _require(batch > 0, f"{op}: batch must be > 0")
+    _require(kv_indptr.numel() == batch + 1 and prefix_lens.numel() == batch,
+             f"{op}: kv_indptr must have batch+1 and prefix_lens batch entries")
+    out = torch.empty_like(q)
+    sh = _stream_handle(stream, q.device)
+    lib = _lib.lib()
+    total_kv = kv_indices.numel()
+    with torch.cuda.device(q.device):
+        need = lib.msgl_prefill_workspace_bytes(batch, total_q, total_kv, hq, k_cache.shape[1], d,
+                                                int(max_len_extend), int(sliding_window_size))
+        ws = _workspace(need, q.device, sh)
+        _lib.check(lib.msgl_paged_prefill_attention(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
+            kv_indptr.data_ptr(), kv_indices.data_ptr(), prefix_lens.data_ptr(), out.data_ptr(),
+            ws.data_ptr(), ws.numel(), batch, total_q, total_kv, hq, k_cache.shape[1], d,
+            k_cache.shape[0], _DTYPES[q.dtype], float(sm_scale), int(max_len_extend),
+            int(bool(is_cross_attention)), int(sliding_window_size), sh))
+    return out
+
+
+def store_kv_cache(k_cache, v_cache, indices, k, v, *, stream=None) -> None:
+    """In place: ``k_cache[indices[r]] = k[r]``, ``v_cache[indices[r]] = v[r]``.
+
+    Signature and checks of the reference op:
+    mini-sglang-mlx-kernel/csrc/bindings.cpp:27-32, csrc/store_kv_cache.cpp:22-63.
+    """
+    op = "store_kv_cache"
+    _require(k_cache.dim() == 3 and v_cache.dim() == 3,
+             f"{op}: k_cache and v_cache must be 3D (num_pages, num_kv_heads, head_dim)")
+    _require(indices.dim() == 1, f"{op}: indices must be 1D")
+    _require(k.dim() == 3 and v.dim() == 3,
+             f"{op}: k and v must be 3D (length, num_kv_heads, head_dim)")
+    _require(k_cache.dtype == v_cache.dtype == k.dtype == v.dtype,
+             f"{op}: k_cache, v_cache, k, v must have the same dtype")
+    _require(indices.dtype == torch.int32, f"{op}: indices must be int32")
+    _require(k_cache.dtype in _DTYPES, f"{op}: unsupported dtype, must be float16 or bfloat16")
+    num_slots, hkv, d = k_cache.shape
+    length = indices.shape[0]
+    _require(d % 4 == 0, f"{op}: head_dim must be a multiple of 4")
+    _require(v_cache.shape == k_cache.shape, f"{op}: v_cache shape must match k_cache")
+    _require(tuple(k.shape) == (length, hkv, d) and tuple(v.shape) == (length, hkv, d),
+             f"{op}: k and v shape must be (length, num_kv_heads, head_dim)")
+    _require(k_cache.is_cuda and all(t.device == k_cache.device for t in (v_cache, indices, k, v)),
+             f"{op}: tensors must live on the same CUDA device")
+    for t in (k_cache, v_cache, k, v):
+        _require(t.stride(2) == 1 and t.stride(1) == d, f"{op}: rows must be dense")
+    _require(k.stride(0) == v.stride(0) and k_cache.stride(0) == v_cache.stride(0),
+             f"{op}: k/v (and the two caches) must share their row stride")
+    _require(indices.is_contiguous(), f"{op}: indices must be contiguous")
+    sh = _stream_handle(stream, k_cache.device)
+    with torch.cuda.device(k_cache.device):
+        _lib.check(_lib.lib().msgl_store_kv_cache(
+            k_cache.data_ptr(), v_cache.data_ptr(), indices.data_ptr(), k.data_ptr(), v.data_ptr(),
+            length, hkv, d, num_slots, k_cache.stride(0), k.stride(0), _DTYPES[k_cache.dtype], sh))
+
+
+def gather_kv_indices(page_table, table_idx, kv_indptr, total_kv: int, *, stream=None):
+    """``kv_indices[kv_indptr[b] + t] = page_table[table_idx[b], t]`` for
+    ``t < kv_indptr[b+1] - kv_indptr[b]``, in one launch.  Device-side form of the
+    per-request loops of AttnBackend.build_*_metadata
+    (mini_sglang_mlx/attention/backend.py:239-244, 279-284)."""
+    op = "gather_kv_indices"
+    _require(page_table.dim() == 2 and page_table.dtype == torch.int32 and page_table.stride(1) == 1,
+             f"{op}: page_table must be a 2D int32 tensor with dense rows")
+    _require(table_idx.dtype == torch.int32 and kv_indptr.dtype == torch.int32,
+             f"{op}: table_idx and kv_indptr must be int32")
+    _require(page_table.is_cuda and table_idx.device == page_table.device
+             and kv_indptr.device == page_table.device, f"{op}: tensors must be on one CUDA device")
+    batch = table_idx.numel()
+    _require(kv_indptr.numel() == batch + 1, f"{op}: kv_indptr must have batch+1 entries")
+    out = torch.empty(int(total_kv), dtype=torch.int32, device=page_table.device)
+    sh = _stream_handle(stream, page_table.device)
+    with torch.cuda.device(page_table.device):
+        _lib.check(_lib.lib().msgl_gather_kv_indices(
+            page_table.data_ptr(), page_table.stride(0), table_idx.contiguous().data_ptr(),
+            kv_indptr.contiguous().data_ptr(), out.data_ptr(), batch, int(total_kv), sh))
+    return out

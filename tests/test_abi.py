@@ -1,0 +1,110 @@
+"""The C-ABI library loads, exports what the header declares and rejects bad
+arguments with the documented status codes — no kernel is launched here."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from mini_sglang_mlx_b200 import _lib
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "msgl_b200.h"
+
+
+def declared_symbols():
+    text = HEADER.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(msgl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    syms = declared_symbols()
+    for name in ("msgl_paged_decode_attention", "msgl_paged_prefill_attention", "msgl_store_kv_cache",
+                 "msgl_decode_workspace_bytes", "msgl_prefill_workspace_bytes",
+                 "msgl_gather_kv_indices", "msgl_last_error_string", "msgl_abi_version"):
+        assert name in syms
+
+
+def test_library_exports_every_declared_symbol():
+    handle = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in declared_symbols():
+        assert hasattr(handle, name), f"{name} declared in the header but not exported"
+    # and the ctypes table covers every declaration
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+
+
+def test_abi_version():
+    assert _lib.lib().msgl_abi_version() == 1
+
+
+def test_decode_workspace_bytes():
+    lib = _lib.lib()
+    # status area + fp32 partials (B,Hq,S,D) + fp32 lse (B,Hq,S)
+    assert lib.msgl_decode_workspace_bytes(8, 16, 128, 32) == 256 + 8 * 16 * 32 * 129 * 4
+    assert lib.msgl_decode_workspace_bytes(0, 16, 128, 32) == 256
+
+
+DEC_OK = dict(batch=2, hq=16, hkv=8, d=128, slots=64, dtype=0, splits=32)
+
+
+def call_decode(**kw):
+    a = dict(DEC_OK, **kw)
+    return _lib.lib().msgl_paged_decode_attention(
+        None, None, None, None, None, None, None, None, 0, a["batch"], a["hq"], a["hkv"], a["d"],
+        a["slots"], a["dtype"], 0.1, a["splits"], None)
+
+
+@pytest.mark.parametrize("kw,code,text", [
+    (dict(d=64), 3, "paged_decode_attention: head_dim must be 128 or 256"),
+    (dict(hq=12, hkv=8), 4, "paged_decode_attention: num_q_heads must be a multiple of num_kv_heads"),
+    (dict(hq=34, hkv=2), 4, "paged_decode_attention: only q_heads/kv_heads <= 16 is supported"),
+    (dict(dtype=9), 2, "paged_decode_attention: unsupported dtype, must be float16 or bfloat16"),
+    (dict(splits=0), 5, "max_kv_splits"),
+    (dict(), 5, "null tensor pointer"),
+])
+def test_decode_rejects_bad_arguments(kw, code, text):
+    assert call_decode(**kw) == code
+    assert text in _lib.last_error()
+
+
+def test_decode_empty_batch_is_a_no_op():
+    assert call_decode(batch=0) == 0
+
+
+def call_prefill(batch=2, total_q=8, hq=32, hkv=8, d=128, dtype=0, window=0):
+    return _lib.lib().msgl_paged_prefill_attention(
+        None, None, None, None, None, None, None, None, None, 0, batch, total_q, 100, hq, hkv, d, 64,
+        dtype, 0.1, 4, 0, window, None)
+
+
+@pytest.mark.parametrize("kw,code,text", [
+    (dict(d=96), 3, "paged_prefill_attention: head_dim must be 128 or 256"),
+    (dict(hq=30), 4, "paged_prefill_attention: num_q_heads must be a multiple of num_kv_heads"),
+    (dict(window=-1), 5, "paged_prefill_attention: sliding_window_size must be >= 0"),
+    (dict(batch=0), 1, "paged_prefill_attention: batch must be > 0"),
+    (dict(dtype=5), 2, "paged_prefill_attention: unsupported dtype"),
+    (dict(), 5, "null tensor pointer"),
+])
+def test_prefill_rejects_bad_arguments(kw, code, text):
+    assert call_prefill(**kw) == code
+    assert text in _lib.last_error()
+
+
+def test_store_rejects_bad_arguments():
+    lib = _lib.lib()
+    assert lib.msgl_store_kv_cache(None, None, None, None, None, 4, 8, 126, 64, 8 * 126, 8 * 126, 0, None) == 1
+    assert "store_kv_cache: head_dim must be a multiple of 4" in _lib.last_error()
+    assert lib.msgl_store_kv_cache(None, None, None, None, None, 4, 8, 128, 64, 8 * 128, 8 * 128, 7, None) == 2
+    assert lib.msgl_store_kv_cache(None, None, None, None, None, 0, 8, 128, 64, 8 * 128, 8 * 128, 0, None) == 0
+
+
+def test_python_ops_refuse_cpu_tensors():
+    import torch
+    from mini_sglang_mlx_b200 import paged_decode_attention
+    q = torch.zeros(1, 2, 128, dtype=torch.bfloat16)
+    kc = torch.zeros(4, 1, 128, dtype=torch.bfloat16)
+    z = torch.zeros(2, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        paged_decode_attention(q, kc, kc, z, z, z[:1], 0.1, 32)
+    with pytest.raises(RuntimeError, match="q must be 3D"):
+        paged_decode_attention(q[0], kc, kc, z, z, z[:1], 0.1, 32)

@@ -1,0 +1,140 @@
+"""store_kv_cache, the page pool and the backend's metadata on the GPU: exact
+(bit-for-bit) against the oracle's scatter and index builders."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import paged_attention_oracle as O
+from tests.helpers import assert_close_to_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("length,hkv,d", [(1, 1, 128), (37, 8, 128), (1000, 4, 128), (64, 2, 256), (5, 3, 100)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scatter_matches_naive_loop(length, hkv, d, dtype):
+    from mini_sglang_mlx_b200 import store_kv_cache
+    g = torch.Generator().manual_seed(length)
+    S = length * 3 + 5
+    kc0 = torch.randn(S, hkv, d, generator=g).to(dtype)
+    vc0 = torch.randn(S, hkv, d, generator=g).to(dtype)
+    k = torch.randn(length, hkv, d, generator=g).to(dtype)
+    v = torch.randn(length, hkv, d, generator=g).to(dtype)
+    idx = torch.randperm(S, generator=g)[:length].int()
+    kc, vc = kc0.clone().cuda(), vc0.clone().cuda()
+    store_kv_cache(kc, vc, idx.cuda(), k.cuda(), v.cuda())
+    O.store_kv_cache_oracle(kc0, vc0, idx, k, v)
+    assert torch.equal(kc.cpu(), kc0) and torch.equal(vc.cpu(), vc0)
+
+
+def test_scatter_from_a_strided_projection_output():
+    # k and v are often two slices of one fused projection: rows are strided
+    from mini_sglang_mlx_b200 import store_kv_cache
+    hkv, d, n = 4, 128, 50
+    kv = torch.randn(n, 2, hkv, d).bfloat16().cuda()
+    k, v = kv[:, 0], kv[:, 1]
+    kc = torch.zeros(200, hkv, d, dtype=torch.bfloat16).cuda()
+    vc = torch.zeros_like(kc)
+    idx = torch.randperm(200)[:n].int().cuda()
+    store_kv_cache(kc, vc, idx, k, v)
+    assert torch.equal(kc[idx.long()], k) and torch.equal(vc[idx.long()], v)
+
+
+def test_store_rejects_mismatched_inputs():
+    from mini_sglang_mlx_b200 import store_kv_cache
+    kc = torch.zeros(8, 2, 128, dtype=torch.bfloat16).cuda()
+    k = torch.zeros(3, 2, 128, dtype=torch.bfloat16).cuda()
+    idx = torch.zeros(3, dtype=torch.int32).cuda()
+    with pytest.raises(RuntimeError, match="indices must be int32"):
+        store_kv_cache(kc, kc.clone(), idx.long(), k, k)
+    with pytest.raises(RuntimeError, match="same dtype"):
+        store_kv_cache(kc, kc.clone(), idx, k.half(), k)
+    with pytest.raises(RuntimeError, match="shape must be"):
+        store_kv_cache(kc, kc.clone(), idx, k[:2], k)
+
+
+class _Cfg:
+    head_dim = 128
+    num_kv_heads = 2
+    num_qo_heads = 8
+
+
+def _backend(num_pages=4096, rows=8, max_seq=2048, layers=2):
+    from mini_sglang_mlx_b200.attention import AttnBackend
+    from mini_sglang_mlx_b200.kvcache import MHAKVCache
+    pool = MHAKVCache(_Cfg.num_kv_heads, layers, _Cfg.head_dim, num_pages + 1, torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    table = torch.stack([torch.randperm(num_pages, generator=g)[:max_seq] for _ in range(rows)]).int().cuda()
+    return AttnBackend(_Cfg, pool, table), pool, table
+
+
+def test_metadata_is_bit_exact_with_the_reference_builders():
+    from mini_sglang_mlx_b200.core import Req
+    be, _, table = _backend()
+    reqs = [Req(table_idx=3, cached_len=100, device_len=164), Req(table_idx=0, cached_len=0, device_len=7),
+            Req(table_idx=5, cached_len=999, device_len=1000)]
+    md = be.build_prefill_metadata(reqs)
+    pos, qo, kvp, idx, pre, mle = O.build_prefill_metadata_oracle(
+        table.cpu().numpy(), [r.table_idx for r in reqs], [r.extend_len for r in reqs],
+        [r.device_len for r in reqs])
+    assert np.array_equal(md.positions.cpu().numpy(), pos)
+    assert np.array_equal(md.qo_indptr.cpu().numpy(), qo)
+    assert np.array_equal(md.kv_indptr.cpu().numpy(), kvp)
+    assert np.array_equal(md.kv_indices.cpu().numpy(), idx)
+    assert np.array_equal(md.prefix_lens.cpu().numpy(), pre)
+    assert md.max_len_extend == mle
+    # virtual K+1-token verify window over the same requests
+    md2 = be.build_prefill_metadata(reqs, extend_lens=[8] * 3, kv_lens=[r.cached_len + 8 for r in reqs])
+    _, qo2, kvp2, idx2, pre2, _ = O.build_prefill_metadata_oracle(
+        table.cpu().numpy(), [r.table_idx for r in reqs], [8] * 3, [r.cached_len + 8 for r in reqs])
+    assert np.array_equal(md2.kv_indices.cpu().numpy(), idx2)
+    assert np.array_equal(md2.prefix_lens.cpu().numpy(), pre2)
+    be.split_policy = "reference"
+    dm = be.build_decode_metadata(reqs)
+    pos, kvp, idx, splits, mx = O.build_decode_metadata_oracle(
+        table.cpu().numpy(), [r.table_idx for r in reqs], [r.device_len for r in reqs],
+        [r.cached_len for r in reqs])
+    assert np.array_equal(dm.positions.cpu().numpy(), pos)
+    assert np.array_equal(dm.kv_indptr.cpu().numpy(), kvp)
+    assert np.array_equal(dm.kv_indices.cpu().numpy(), idx)
+    assert np.array_equal(dm.num_kv_splits.cpu().numpy(), splits)
+    assert dm.max_kv_splits == mx
+
+
+def test_backend_prefill_then_decode_steps_match_the_oracle():
+    """Chunked prefill of three requests, then two decode steps, through
+    AttnBackend.forward (store K/V, then attention) on layer 1 of the pool."""
+    from mini_sglang_mlx_b200.core import Batch, BatchPhase, Req
+    be, pool, table = _backend()
+    g = torch.Generator().manual_seed(2)
+    hq, hkv, d = _Cfg.num_qo_heads, _Cfg.num_kv_heads, _Cfg.head_dim
+    layer = 1
+    # a shadow pool on the host, written by the oracle's scatter
+    kc = torch.zeros(pool.num_pages, hkv, d, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    reqs = [Req(table_idx=1, cached_len=0, device_len=300), Req(table_idx=4, cached_len=0, device_len=45),
+            Req(table_idx=6, cached_len=0, device_len=1)]
+    phases = [BatchPhase.PREFILL, BatchPhase.DECODE, BatchPhase.DECODE]
+    for phase in phases:
+        n = sum(r.extend_len for r in reqs)
+        q = torch.randn(n, hq, d, generator=g).bfloat16()
+        k = torch.randn(n, hkv, d, generator=g).bfloat16()
+        v = torch.randn(n, hkv, d, generator=g).bfloat16()
+        out_loc = torch.cat([table[r.table_idx, r.cached_len:r.device_len] for r in reqs])
+        batch = Batch(reqs=reqs, phase=phase, out_loc=out_loc)
+        be.prepare_metadata(batch)
+        out = be.forward(q.cuda(), k.cuda(), v.cuda(), layer, batch)
+        O.store_kv_cache_oracle(kc, vc, out_loc.cpu(), k, v)
+        md = batch.attn_metadata
+        if phase == BatchPhase.PREFILL:
+            ref = O.paged_prefill_attention_oracle(q, kc, vc, md.qo_indptr, md.kv_indptr, md.kv_indices,
+                                                   md.prefix_lens, be.sm_scale)
+        else:
+            ref = O.paged_decode_attention_oracle(q, kc, vc, md.kv_indptr, md.kv_indices, be.sm_scale)
+        assert_close_to_oracle(out, ref, f"backend {phase}")
+        for r in reqs:
+            r.complete_one()
+    assert torch.equal(pool.k_cache(layer).cpu(), kc) and torch.equal(pool.v_cache(layer).cpu(), vc)
+    assert torch.count_nonzero(pool.k_cache(0)) == 0
