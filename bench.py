@@ -1,0 +1,526 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A step is one pass of the operator over one batch of seeded synthetic input
+with the shape of a benchmark configuration.  The headline workload is the
+chunked-prefill configuration (``cfg2``: Qwen3-8B shape, 4 sequences, cached
+prefix U{0..4096} + a 512-token chunk, causal), reported in TFLOP/s; the same
+JSON line carries the long-context decode configuration (``cfg5a``) in GB/s
+under ``"decode"``.  Under torchrun every rank runs its own batch (weak
+scaling, sharding by request: no collective on the data path); ``e2e`` at
+N > 1 adds the NCCL all-gather that reassembles the outputs.
+
+``value``       kernel-only throughput, inputs resident in HBM, CUDA events per step,
+                L2 flushed between steps; max over ranks of the summed time.
+``e2e``         the same metric through ``AttnBackend.forward`` with HOST buffers:
+                pinned host -> device copies of q/k/v and metadata, K/V store,
+                attention, device -> pinned host copy of the output, all timed.
+``roofline``    algorithmic flops (or bytes) / mean kernel time against the measured peak.
+``cpu_baseline``the CPU restatement (gather pages, fp32 SDPA) timed on the host cores.
+
+``--impl reference`` times that CPU path alone (the reference's Metal kernels
+need macOS and its MLX CPU path needs the ``mlx`` package, neither is
+available here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+METRIC = "paged decode HBM GB/s + prefill TFLOP/s vs roofline at 1/2/4/8 B200"
+L2_FLUSH_BYTES = 256 << 20
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    _NAMES = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+              0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in self._NAMES.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------- workloads
+BATCH_OVERRIDE = None  # --batch: smaller batch of the same configuration (profiling captures)
+
+
+def make_workload(name: str, device, rank: int):
+    from mini_sglang_mlx_b200 import synthetic as S
+    seed_shift = 1000 * rank
+    kw = {} if BATCH_OVERRIDE is None else {"batch": BATCH_OVERRIDE}
+    if name == "cfg1":
+        return S.cfg1_decode(seed=101 + seed_shift, device=device, **kw)
+    if name == "cfg2":
+        return S.cfg2_prefill(seed=202 + seed_shift, device=device, **kw)
+    if name == "cfg3":
+        return S.cfg3_window_block(seed=303 + seed_shift, device=device, **kw)
+    if name == "cfg4":
+        return S.cfg4_verify(seed=404 + seed_shift, device=device, **kw)
+    if name == "cfg5a":
+        from mini_sglang_mlx_b200.attention import compute_num_kv_splits
+        w = S.cfg5a_decode(seed=505 + seed_shift, device=device, **kw)
+        splits = compute_num_kv_splits(w.kv_lens, w.hkv)
+        w.num_kv_splits = torch.tensor(splits, dtype=torch.int32, device=device)
+        return w
+    if name.startswith("cfg5b"):
+        _, c, p = name.split("_")
+        return S.cfg5b_prefill_point(int(c), int(p), seed=606 + seed_shift, device=device)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def run_op(w):
+    from mini_sglang_mlx_b200 import paged_decode_attention, paged_prefill_attention
+    if w.kind == "decode":
+        return paged_decode_attention(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices,
+                                      w.num_kv_splits, w.sm_scale, w.max_kv_splits)
+    return paged_prefill_attention(w.q, w.k_cache, w.v_cache, w.qo_indptr, w.kv_indptr, w.kv_indices,
+                                   w.prefix_lens, w.sm_scale, w.max_len_extend,
+                                   is_cross_attention=w.is_cross_attention,
+                                   sliding_window_size=w.sliding_window_size)
+
+
+def launches_per_step(w) -> int:
+    from mini_sglang_mlx_b200 import _lib
+    if w.kind == "decode":
+        return 2
+    need = _lib.lib().msgl_prefill_workspace_bytes(w.batch, w.q.shape[0], w.kv_indices.numel(), w.hq,
+                                                   w.hkv, w.head_dim, w.max_len_extend,
+                                                   w.sliding_window_size)
+    return 2 if need > 256 else 1
+
+
+def barrier(dist_on: bool):
+    if dist_on:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, dist_on: bool) -> float:
+    if not dist_on:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_kernel_steps(w, steps: int, warmup: int, dist_on: bool, flush):
+    """Sum of per-step device times (ms) of `steps` operator calls, L2 flushed before each."""
+    for _ in range(warmup):
+        flush.zero_()
+        run_op(w)
+    barrier(dist_on)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush.zero_()
+        starts[i].record()
+        run_op(w)
+        ends[i].record()
+    barrier(dist_on)
+    per = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    return sum(per), per
+
+
+# ----------------------------------------------------------------------------- end to end
+class _ModelCfg:
+    def __init__(self, w):
+        self.head_dim, self.num_kv_heads, self.num_qo_heads = w.head_dim, w.hkv, w.hq
+
+
+def build_e2e(w, device):
+    """A one-layer pool holding the workload's KV, a per-token slot table, the requests, and
+    pinned host buffers with this step's q/k/v."""
+    from mini_sglang_mlx_b200.attention import AttnBackend
+    from mini_sglang_mlx_b200.core import Batch, BatchPhase, Req
+    from mini_sglang_mlx_b200.kvcache import MHAKVCache
+    num_slots = w.k_cache.shape[0]
+    pool = MHAKVCache.__new__(MHAKVCache)
+    # adopt the workload's tensors as layer 0 of the pool (no second copy of a 38 GB pool)
+    pool._num_layers, pool._dtype = 1, w.k_cache.dtype
+    pool._storage_shape = tuple(w.k_cache.shape)
+    pool._k_buffer, pool._v_buffer = [w.k_cache], [w.v_cache]
+    max_len = max(w.kv_lens)
+    table = torch.zeros((w.batch, max_len), dtype=torch.int32, device=device)
+    indptr = w.kv_indptr.tolist()
+    for b in range(w.batch):
+        table[b, : w.kv_lens[b]] = w.kv_indices[indptr[b]:indptr[b + 1]]
+    be = AttnBackend(_ModelCfg(w), pool, table)
+    if w.kind == "decode":
+        reqs = [Req(table_idx=b, cached_len=w.kv_lens[b] - 1, device_len=w.kv_lens[b]) for b in range(w.batch)]
+        phase = BatchPhase.DECODE
+    else:
+        reqs = [Req(table_idx=b, cached_len=w.kv_lens[b] - w.q_lens[b], device_len=w.kv_lens[b])
+                for b in range(w.batch)]
+        phase = BatchPhase.PREFILL
+    out_loc = torch.cat([table[r.table_idx, r.cached_len:r.device_len] for r in reqs]).contiguous()
+    n = out_loc.numel()
+    host = dict(
+        q=w.q.cpu().pin_memory(),
+        k=w.k_cache[out_loc.long()].cpu().pin_memory(),
+        v=w.v_cache[out_loc.long()].cpu().pin_memory(),
+        out_loc=out_loc.cpu().pin_memory(),
+        out=torch.empty(w.q.shape, dtype=w.q.dtype).pin_memory())
+    dev = dict(q=torch.empty_like(w.q), k=torch.empty((n, w.hkv, w.head_dim), dtype=w.q.dtype, device=device),
+               v=torch.empty((n, w.hkv, w.head_dim), dtype=w.q.dtype, device=device),
+               out_loc=torch.empty(n, dtype=torch.int32, device=device))
+    batch = Batch(reqs=reqs, phase=phase)
+    return be, batch, host, dev
+
+
+def e2e_step(w, be, batch, host, dev, gather=None):
+    for key in ("q", "k", "v", "out_loc"):
+        dev[key].copy_(host[key], non_blocking=True)
+    batch.out_loc = dev["out_loc"]
+    be.prepare_metadata(batch)
+    out = be.forward(dev["q"], dev["k"], dev["v"], 0, batch,
+                     is_cross_attention=w.is_cross_attention, sliding_window_size=w.sliding_window_size)
+    if gather is not None:
+        out = gather(out)
+    host["out"].copy_(out[: host["out"].shape[0]], non_blocking=True)
+
+
+def e2e_bytes(w, host, batch):
+    md = 4 * (3 * (w.batch + 1) + 2 * w.batch)  # pointer arrays, table ids, prefix lens / splits
+    bi = sum(host[k].numel() * host[k].element_size() for k in ("q", "k", "v", "out_loc")) + md
+    bo = host["out"].numel() * host["out"].element_size()
+    return bi, bo
+
+
+def time_e2e(w, device, steps, warmup, dist_on, world):
+    be, batch, host, dev = build_e2e(w, device)
+    gather = None
+    if dist_on and world > 1:
+        def gather(out):
+            full = out.new_empty((world * out.shape[0], *out.shape[1:]))
+            torch.distributed.all_gather_into_tensor(full, out.contiguous())
+            return full
+    for _ in range(warmup):
+        e2e_step(w, be, batch, host, dev, gather)
+    barrier(dist_on)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        e2e_step(w, be, batch, host, dev, gather)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result before its next step
+    end.record()
+    barrier(dist_on)
+    ms = start.elapsed_time(end)
+    bi, bo = e2e_bytes(w, host, batch)
+    return ms, bi, bo
+
+
+# ----------------------------------------------------------------------------- CPU baseline
+def cpu_units(w):
+    """(sequence, kv head) pairs: the unit the CPU path is sampled in."""
+    return [(b, h) for b in range(w.batch) for h in range(w.hkv)]
+
+
+def cpu_run_units(wc, units):
+    """The CPU restatement (gather pages -> fp32 SDPA with the explicit mask) on some units.
+    Returns the flops it performed."""
+    from oracle import paged_attention_oracle as O
+    g = wc.hq // wc.hkv
+    flops = 0
+    W = wc.sliding_window_size
+    for (b, h) in units:
+        s, e = int(wc.kv_indptr[b]), int(wc.kv_indptr[b + 1])
+        rows = wc.kv_indices[s:e].long()
+        k = wc.k_cache[rows, h:h + 1]
+        v = wc.v_cache[rows, h:h + 1]
+        L = e - s
+        if wc.kind == "decode":
+            q = wc.q[b:b + 1, h * g:(h + 1) * g]
+            O._attend(q.float(), k.float(), v.float(), wc.sm_scale, None)
+            flops += 4 * wc.head_dim * g * L
+        else:
+            qs, qe = int(wc.qo_indptr[b]), int(wc.qo_indptr[b + 1])
+            pre = int(wc.prefix_lens[b])
+            for q0 in range(qs, qe, 1024):
+                q1 = min(qe, q0 + 1024)
+                mask = O.visibility_mask(q1 - q0, L, pre, is_cross_attention=wc.is_cross_attention,
+                                         sliding_window_size=W, q_offset=q0 - qs)
+                O._attend(wc.q[q0:q1, h * g:(h + 1) * g].float(), k.float(), v.float(), wc.sm_scale, mask)
+                flops += 4 * wc.head_dim * g * int(mask.sum())
+    return flops
+
+
+def cpu_copy_of(w):
+    """Host copy of a workload holding only the slots it touches (re-indexed densely)."""
+    import copy
+    wc = copy.copy(w)
+    idx = w.kv_indices.long()
+    uniq, inv = torch.unique(idx, return_inverse=True)
+    wc.k_cache = w.k_cache[uniq].cpu()
+    wc.v_cache = w.v_cache[uniq].cpu()
+    wc.kv_indices = inv.to(torch.int32).cpu()
+    for name in ("q", "kv_indptr", "qo_indptr", "prefix_lens"):
+        t = getattr(w, name)
+        if t is not None:
+            setattr(wc, name, t.cpu())
+    return wc
+
+
+def unit_of(w):
+    return ("TFLOP/s", 1e12) if w.kind == "prefill" else ("GB/s", 1e9)
+
+
+def cpu_work(w, units, flops):
+    if w.kind == "prefill":
+        return flops
+    g = w.hq // w.hkv
+    return sum(2 * w.kv_lens[b] * w.head_dim * 2 + 4 * w.kv_lens[b] + 2 * g * w.head_dim * 2 for b, _ in units)
+
+
+def cpu_baseline(w, budget_s: float = 12.0):
+    wc = cpu_copy_of(w)
+    units = cpu_units(wc)
+    cores = torch.get_num_threads()
+    cpu_run_units(wc, units[:1])  # warm-up
+    t0 = time.perf_counter()
+    done, work = 0, 0.0
+    while time.perf_counter() - t0 < budget_s:
+        u = units[done % len(units)]
+        fl = cpu_run_units(wc, [u])
+        work += cpu_work(wc, [u], fl)
+        done += 1
+    dt = time.perf_counter() - t0
+    unit, div = unit_of(w)
+    return {"value": work / dt / div, "unit": unit, "cores": cores, "kind": "port",
+            "sample": f"{done} (sequence, kv-head) units of {w.name} (the batch has {len(units)}; "
+                      f"cycled), gather pages then fp32 SDPA on torch CPU, {dt:.1f} s"}
+
+
+# ----------------------------------------------------------------------------- arms
+def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, peak_kind, with_e2e=True):
+    w = make_workload(name, device, rank)
+    unit, div = unit_of(w)
+    work = w.algorithmic_flops() if w.kind == "prefill" else w.algorithmic_bytes()
+    big = w.kind == "decode" and w.algorithmic_bytes() > 4 * L2_FLUSH_BYTES
+    fl = torch.empty(1, dtype=torch.uint8, device=device) if big else flush
+    total_ms, per = time_kernel_steps(w, steps, warmup, dist_on, fl)
+    total_ms = max_over_ranks(total_ms, dist_on)
+    work_all = work
+    if dist_on:
+        t = torch.tensor([float(work)], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t)
+        work_all = float(t.item())
+    value = work_all * steps / (total_ms * 1e-3) / div
+    own = work * steps / (sum(per) * 1e-3) / div
+    if w.kind == "prefill":
+        peak = peaks["bf16_tflops"]
+        roof = {"bound": "tensor", "achieved": own, "peak": peak, "unit": "TFLOP/s",
+                "frac": own / peak, "traffic": None, "peak_source": f"{peak_kind} burst bf16"}
+    else:
+        peak = peaks["hbm_gbs"]
+        roof = {"bound": "hbm", "achieved": own, "peak": peak, "unit": "GB/s", "frac": own / peak,
+                "traffic": None, "peak_source": f"{peak_kind} copy bandwidth"}
+    res = {"workload": w.name, "value": value, "unit": unit, "ms_per_step": total_ms / steps,
+           "median_ms": statistics.median(per), "min_ms": min(per), "roofline": roof,
+           "algorithmic_bytes": w.algorithmic_bytes(), "algorithmic_flops": w.algorithmic_flops(),
+           "gpu_launches": launches_per_step(w) * steps,
+           "l2": "inputs larger than L2" if big else "flushed between steps (256 MiB write)"}
+    if with_e2e:
+        e_steps = max(3, min(steps, 50))
+        ms, bi, bo = time_e2e(w, device, e_steps, min(warmup, 5), dist_on, world)
+        ms = max_over_ranks(ms, dist_on)
+        res["e2e"] = {"value": work_all * e_steps / (ms * 1e-3) / div, "unit": unit,
+                      "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo, "steps": e_steps,
+                      "ms_per_step": ms / e_steps}
+    return w, res
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist_on = world > 1
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if dist_on:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    peaks, peak_kind = load_peaks()
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+
+    with ClockSampler(local) as clocks:
+        w, main = measure(args.workload, device, rank, world, args.steps, args.warmup, dist_on, flush,
+                          peaks, peak_kind, with_e2e=not args.no_e2e)
+        extra = {}
+        if args.workload == "cfg2" and not args.no_decode:
+            del w
+            torch.cuda.empty_cache()
+            dsteps = max(3, min(args.steps, 20))
+            w2, dec = measure("cfg5a", device, rank, world, dsteps, 3, dist_on, flush, peaks, peak_kind,
+                              with_e2e=False)
+            dec["steps"] = dsteps
+            extra["decode"] = dec
+            del w2
+            torch.cuda.empty_cache()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(make_workload(args.workload, device, rank))
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": main["value"], "unit": main["unit"], "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": main["workload"], "sharding": "by request, one batch per GPU",
+                       "l2": main["l2"], "page_size": 16, "index_granularity": "per-token slot ids",
+                       "median_ms": main["median_ms"], "min_ms": main["min_ms"],
+                       "algorithmic_flops_per_step": main["algorithmic_flops"],
+                       "algorithmic_bytes_per_step": main["algorithmic_bytes"]},
+            "clocks": clocks.summary(), "e2e": main.get("e2e"), "gpu_launches": main["gpu_launches"],
+            "roofline": main["roofline"], "cpu_baseline": cpu,
+        }
+        line.update(extra)
+        print(json.dumps(line))
+    if dist_on:
+        torch.distributed.destroy_process_group()
+
+
+def run_reference(args):
+    """The CPU path the reference's own tests use as ground truth (gather pages, SDPA), as a
+    torch-CPU restatement: MLX is not installable here and the Metal kernels need macOS."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    from mini_sglang_mlx_b200 import synthetic as S
+    if args.workload == "cfg2":
+        w = S.cfg2_prefill(device=device) if device == "cuda" else S.cfg2_prefill(device="cpu")
+    else:
+        w = make_workload(args.workload, device, 0)
+    wc = cpu_copy_of(w)
+    units = cpu_units(wc)
+    cores = torch.get_num_threads()
+    # size the per-step sample so that warmup + steps fit in about two minutes
+    t0 = time.perf_counter()
+    cpu_run_units(wc, units[:1])
+    t_unit = time.perf_counter() - t0
+    per_step = max(1, min(len(units), int(120.0 / max(1, args.steps + args.warmup) / max(t_unit, 1e-4))))
+    sample = units[:per_step]
+    for _ in range(args.warmup):
+        cpu_run_units(wc, sample)
+    t0 = time.perf_counter()
+    work = 0.0
+    for _ in range(args.steps):
+        fl = cpu_run_units(wc, sample)
+        work += cpu_work(wc, sample, fl)
+    dt = time.perf_counter() - t0
+    unit, div = unit_of(w)
+    value = work / dt / div
+    desc = (f"{per_step} of {len(units)} (sequence, kv-head) units of {w.name} per step, "
+            f"gather pages then fp32 SDPA on torch CPU")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": unit,
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "note": "reference Metal kernels need macOS; MLX CPU backend not "
+                   "installable here; this is the torch-CPU restatement of its gather-then-SDPA path"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--no-decode", action="store_true", help="skip the cfg5a decode measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the configuration's batch size (small profiling captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    global BATCH_OVERRIDE
+    BATCH_OVERRIDE = args.batch
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
