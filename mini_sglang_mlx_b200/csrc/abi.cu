@@ -10,6 +10,7 @@
 #include "../../include/msgl_b200.h"
 #include "decode_splitkv.cuh"
 #include "prefill_mma.cuh"
+#include "prefill_tc.cuh"
 
 namespace {
 
@@ -58,9 +59,11 @@ struct PrefillPlan {
 
 PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int hkv, int head_dim,
                          int max_len_extend, int window, int sms) {
+  // One CTA of the tensor-core kernel per SM: the key range is split only when the query
+  // tiles alone cannot give every SM a CTA; then about two CTAs per SM are made.
   PrefillPlan pl{};
   const int G = hq / hkv;
-  const int BM = msgl::kMmaBM;
+  const int BM = msgl::kTcBM;
   const int64_t qtiles = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, 0);
   int64_t visible = total_kv;
   if (window > 0) {
@@ -68,11 +71,11 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
     if (w < visible) visible = w;
   }
   pl.kv_chunk = 0;
-  if (qtiles * hkv < 2LL * sms && visible > 0) {
+  if (qtiles * hkv < sms && visible > 0) {
     const int64_t nqt_max = (static_cast<int64_t>(max_len_extend) * G + BM - 1) / BM;
-    int64_t chunk = visible * nqt_max * hkv / (4LL * sms);
+    int64_t chunk = visible * nqt_max * hkv / (2LL * sms);
     if (chunk < 256) chunk = 256;
-    chunk = (chunk + 63) / 64 * 64;
+    chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
   }
   pl.items = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, pl.kv_chunk);
@@ -292,22 +295,23 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
   p.kv_chunk = pl.kv_chunk;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  constexpr int smem = msgl::kMmaStages * 2 * msgl::kMmaBN * 256;
   dim3 grid(static_cast<unsigned>(pl.items), num_kv_heads);
   dim3 mgrid(total_q, num_q_heads);
   cudaError_t e;
   if (dtype == MSGL_DTYPE_BF16) {
-    auto k = msgl::prefill_mma_kernel<__nv_bfloat16, 128>;
-    if ((e = allow_smem(k, smem)) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
-    k<<<grid, msgl::kMmaWarps * 32, smem, s>>>(p);
+    auto k = msgl::prefill_tc_kernel<__nv_bfloat16>;
+    if ((e = allow_smem(k, msgl::kTcSmemBytes)) != cudaSuccess)
+      return cuda_fail("paged_prefill_attention", e);
+    k<<<grid, msgl::kTcThreads, msgl::kTcSmemBytes, s>>>(p);
     if (pl.kv_chunk > 0)
-      msgl::prefill_merge_kernel<__nv_bfloat16, 128, msgl::kMmaBM><<<mgrid, 128, 0, s>>>(p);
+      msgl::prefill_merge_kernel<__nv_bfloat16, 128, msgl::kTcBM><<<mgrid, 128, 0, s>>>(p);
   } else {
-    auto k = msgl::prefill_mma_kernel<__half, 128>;
-    if ((e = allow_smem(k, smem)) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
-    k<<<grid, msgl::kMmaWarps * 32, smem, s>>>(p);
+    auto k = msgl::prefill_tc_kernel<__half>;
+    if ((e = allow_smem(k, msgl::kTcSmemBytes)) != cudaSuccess)
+      return cuda_fail("paged_prefill_attention", e);
+    k<<<grid, msgl::kTcThreads, msgl::kTcSmemBytes, s>>>(p);
     if (pl.kv_chunk > 0)
-      msgl::prefill_merge_kernel<__half, 128, msgl::kMmaBM><<<mgrid, 128, 0, s>>>(p);
+      msgl::prefill_merge_kernel<__half, 128, msgl::kTcBM><<<mgrid, 128, 0, s>>>(p);
   }
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   return MSGL_OK;

@@ -1,0 +1,616 @@
+// Paged prefill / extend / verify attention on the 5th-generation tensor
+// cores: tcgen05.mma with accumulators in tensor memory (TMEM), sm_100a only.
+//
+// One CTA owns 256 GQA-packed query rows of one KV head (two sub-tiles of 128
+// rows) and walks the visible key range in tiles of 128 tokens.
+//
+//   warps 0-3   softmax group 0: thread r owns row r of sub-tile 0 (TMEM lane r)
+//   warps 4-7   softmax group 1: the same for sub-tile 1
+//   warp  8     MMA issuer (one lane issues every tcgen05.mma / commit)
+//   warps 9-12  producers: gather Q rows and paged K/V token rows with 16-byte
+//               cp.async into 128-byte-swizzled shared-memory tiles
+//
+// Per key tile j and sub-tile i:  S_i = Q_i K_j^T  (SS MMA, fp32 in TMEM)
+//   -> softmax group i reads S_i (tcgen05.ld), applies the mask on boundary
+//      tiles, keeps a running reference max (O is rescaled lazily, only when
+//      the max grows by more than 2^8), writes P_i as bf16 over the S_i columns
+//      (tcgen05.st)
+//   -> O_i += P_i V_j  (TS MMA: A from TMEM, V as an MN-major shared operand).
+// The issue order PV0_j, S0_{j+1}, PV1_j, S1_{j+1} keeps the tensor pipe busy
+// on one sub-tile while the other is in softmax.  All hand-offs are mbarriers;
+// every wait is bounded and reports through the status word instead of
+// hanging.  TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512).
+//
+// Shared-memory tile layout (Q sub-tile, K tile and V tile alike): two
+// 16 KB halves, half h holding elements [64h, 64h+64) of every row; inside a
+// half row r sits at (r/8)*1024 + (r%8)*128 and its 16-byte chunk c at
+// position c ^ (r%8).  This is the canonical 128-byte-swizzle layout, K-major
+// for Q and K (rows = M/N index) and MN-major for V (rows = K index).
+#pragma once
+
+#include <type_traits>
+
+#include "prefill_tiles.cuh"
+
+namespace msgl {
+
+constexpr int kTcBM = 256;        // packed query rows per CTA
+constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
+constexpr int kTcBN = 128;        // key tokens per tile
+constexpr int kTcStages = 2;      // K ring and V ring depth
+constexpr int kTcThreads = 13 * 32;
+constexpr int kTcTileBytes = 128 * 256;                      // one 128-row x 128-element tile
+constexpr int kTcSmemBytes = (2 + 2 * kTcStages) * kTcTileBytes + 1024;  // + alignment slack
+constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait: false after kTcWaitCycles or once another thread has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0 || clock64() - t0 > kTcWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+// Warp-uniform form: every lane waits, the warp agrees on the outcome, so that the
+// warp-collective instructions that follow are executed by all lanes or by none.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
+}
+// Arrive on `bar` once all cp.async copies issued so far by this thread have landed.
+__device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+// lbo / sbo are byte offsets (leading / stride dimension).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulate, A/B both bf16 or both f16,
+// A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), M = 128, N = 128.
+template <typename T>
+__device__ __forceinline__ uint32_t idesc_m128n128(uint32_t b_mn) {
+  const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((128u >> 3) << 17) |
+         ((128u >> 4) << 24);
+}
+
+// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` (0..127) inside a tile.
+__device__ __forceinline__ uint32_t tc_tile_offset(int row, int chunk) {
+  return static_cast<uint32_t>(((chunk >> 3) << 14) + ((row >> 3) << 10) + ((row & 7) << 7) +
+                               (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+struct TcBarriers {
+  uint64_t q_full;
+  uint64_t k_full[kTcStages], k_empty[kTcStages];
+  uint64_t v_full[kTcStages], v_empty[kTcStages];
+  uint64_t s_full[2], p_full[2], pv_done[2];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const PrefillParams p) {
+  constexpr int HD = 128;
+  constexpr int BM = kTcBM, SUB = kTcSub, BN = kTcBN;
+  constexpr int NPROD = 128;  // producer threads
+
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ TcBarriers bars;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y;
+  const int G = p.group;
+
+  int b, local, base;
+  const int item = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  if (!find_item<kTcThreads>(p, item, BM, b, local, base)) return;  // uniform for the block
+  const SeqShape sq = load_seq_shape(p, b, BM);
+  const int qt = local / sq.nsplit;
+  const int split = local % sq.nsplit;
+  if (p.plan && local == 0 && h == 0 && tid == 0) {
+    p.plan[2 * b] = base;
+    p.plan[2 * b + 1] = sq.nsplit;
+  }
+
+  // ---- geometry of the CTA's rows and of each sub-tile
+  const int pk0 = qt * BM;
+  const int rows_valid = min(BM, sq.tq * G - pk0);              // >= 1
+  const int nsub = rows_valid > SUB ? 2 : 1;
+  const int tok_first = pk0 / G;
+  const int s_lo = p.kv_chunk > 0 ? sq.lo + split * p.kv_chunk : 0;
+  const int s_hi = p.kv_chunk > 0 ? sq.lo + (split + 1) * p.kv_chunk : 0x7fffffff;  // exclusive
+  int kv_lo = p.window > 0 ? max(0, sq.prefix + tok_first - p.window + 1) : 0;
+  kv_lo = max(kv_lo, s_lo);
+  kv_lo = (kv_lo / BN) * BN;
+  int ntiles_sub[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int last_row = min(rows_valid, (i + 1) * SUB) - 1;     // last valid row of the sub-tile
+    const int tok_last = (pk0 + last_row) / G;
+    int hi = p.is_cross ? sq.L : min(sq.L, sq.prefix + tok_last + 1);
+    hi = min(hi, s_hi);
+    ntiles_sub[i] = (i < nsub && hi > kv_lo) ? ceil_div(hi - kv_lo, BN) : 0;
+  }
+  const int ntiles = max(ntiles_sub[0], ntiles_sub[1]);
+  // keys past kv_hi_load are never fetched (zero rows in the tile)
+  int kv_hi_load = p.is_cross ? sq.L : min(sq.L, sq.prefix + (pk0 + rows_valid - 1) / G + 1);
+  kv_hi_load = min(kv_hi_load, s_hi);
+
+  // ---- shared-memory carve-up (1024-byte aligned tiles)
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem0;                                   // 2 sub-tiles
+  const uint32_t k_smem = smem0 + 2 * kTcTileBytes;                // kTcStages tiles
+  const uint32_t v_smem = k_smem + kTcStages * kTcTileBytes;       // kTcStages tiles
+
+  const uint32_t bar_q = smem_u32(&bars.q_full);
+  auto bar_kf = [&](int s) { return smem_u32(&bars.k_full[s]); };
+  auto bar_ke = [&](int s) { return smem_u32(&bars.k_empty[s]); };
+  auto bar_vf = [&](int s) { return smem_u32(&bars.v_full[s]); };
+  auto bar_ve = [&](int s) { return smem_u32(&bars.v_empty[s]); };
+  auto bar_sf = [&](int i) { return smem_u32(&bars.s_full[i]); };
+  auto bar_pf = [&](int i) { return smem_u32(&bars.p_full[i]); };
+  auto bar_pv = [&](int i) { return smem_u32(&bars.pv_done[i]); };
+
+  if (tid == 0) {
+    s_abort = 0;
+    mbar_init(bar_q, NPROD);
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(bar_kf(s), NPROD);
+      mbar_init(bar_ke(s), 1);
+      mbar_init(bar_vf(s), NPROD);
+      mbar_init(bar_ve(s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_sf(i), 1);
+      mbar_init(bar_pf(i), SUB);
+      mbar_init(bar_pv(i), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(&s_tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp >= 9) {
+    // =========================================================== producers
+    const int ptid = tid - 9 * 32;         // 0..127
+    const int chunk = ptid & 15;           // 16-byte chunk of a 256-byte row
+    const int rsub = ptid >> 4;            // 0..7: row inside a group of 8
+    const T* __restrict__ q = static_cast<const T*>(p.q);
+    const unsigned char* __restrict__ kbase = static_cast<const unsigned char*>(p.k_cache);
+    const unsigned char* __restrict__ vbase = static_cast<const unsigned char*>(p.v_cache);
+    const int64_t slot_stride = static_cast<int64_t>(p.hkv) * (HD * 2);
+    const int64_t head_off = static_cast<int64_t>(h) * (HD * 2);
+
+    // Q: rows_valid packed rows, the rest zero
+    for (int i = 0; i < BM / 8; ++i) {
+      const int row = i * 8 + rsub;      // 0..255
+      if (row >= nsub * SUB) break;
+      const int pk = pk0 + row;
+      const int tl = pk / G, g = pk - tl * G;
+      const bool ok = row < rows_valid;
+      const int64_t off =
+          ok ? ((static_cast<int64_t>(sq.q_begin + tl) * p.hq + static_cast<int64_t>(h) * G + g) * HD)
+             : 0;
+      cp_async_16(q_smem + (row >> 7) * kTcTileBytes + tc_tile_offset(row & 127, chunk),
+                  reinterpret_cast<const unsigned char*>(q + off) + chunk * 16, ok ? 16 : 0);
+    }
+    cp_async_mbar_arrive(bar_q);
+
+    int slots[16];
+    auto load_slots = [&](int tile) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = kv_lo + tile * BN + i * 8 + rsub;
+        int slot = -1;
+        if (tile < ntiles && t < kv_hi_load) {
+          slot = p.kv_indices[sq.kv_begin + t];
+          if (slot < 0 || static_cast<int64_t>(slot) >= p.num_slots) {
+            if (p.status) atomicExch(p.status, 2);
+            slot = -1;
+          }
+        }
+        slots[i] = slot;
+      }
+    };
+    auto issue = [&](uint32_t dst, const unsigned char* src_base) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int row = i * 8 + rsub;
+        const bool ok = slots[i] >= 0;
+        const int64_t off =
+            (ok ? static_cast<int64_t>(slots[i]) * slot_stride + head_off : 0) + chunk * 16;
+        cp_async_16(dst + tc_tile_offset(row, chunk), src_base + off, ok ? 16 : 0);
+      }
+    };
+    load_slots(0);
+    bool alive = true;
+    for (int j = 0; j < ntiles && alive; ++j) {
+      const int s = j % kTcStages;
+      const uint32_t par = ((j / kTcStages) & 1) ^ 1;
+      alive = mbar_wait_warp(bar_ke(s), par, abort_flag);
+      if (!alive) break;
+      issue(k_smem + s * kTcTileBytes, kbase);
+      cp_async_mbar_arrive(bar_kf(s));
+      alive = mbar_wait_warp(bar_ve(s), par, abort_flag);
+      if (!alive) break;
+      issue(v_smem + s * kTcTileBytes, vbase);
+      cp_async_mbar_arrive(bar_vf(s));
+      load_slots(j + 1);
+    }
+    cp_async_wait<0>();
+    if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);
+  } else if (warp == 8) {
+    // =========================================================== MMA issuer
+    const uint32_t idesc_s = idesc_m128n128<T>(0);
+    const uint32_t idesc_pv = idesc_m128n128<T>(1);
+    bool alive = true;
+    auto issue_s = [&](int i, int stage) {
+      // S_i = Q_i K^T : 8 k-steps of 16 elements; both operands K-major
+      if (lane == 0) {
+        const uint32_t qa = q_smem + i * kTcTileBytes;
+        const uint32_t kb = k_smem + stage * kTcTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t koff = (ks >> 2) * 16384 + (ks & 3) * 32;
+          tc_mma_ss(tmem + i * 128, smem_desc_sw128(qa + koff, 16, 1024),
+                    smem_desc_sw128(kb + koff, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(bar_sf(i));
+      }
+      __syncwarp();
+    };
+    auto issue_pv = [&](int i, int stage, bool first) {
+      // O_i (+)= P_i V : 8 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
+      if (lane == 0) {
+        const uint32_t vb = v_smem + stage * kTcTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          tc_mma_ts(tmem + 256 + i * 128, tmem + i * 128 + ks * 8,
+                    smem_desc_sw128(vb + ks * 2048, 16384, 1024), idesc_pv,
+                    (first && ks == 0) ? 0u : 1u);
+        }
+        tc_commit(bar_pv(i));
+      }
+      __syncwarp();
+    };
+    if (ntiles > 0) {
+      alive = mbar_wait_warp(bar_q, 0, abort_flag) && mbar_wait_warp(bar_kf(0), 0, abort_flag);
+      if (alive) {
+        fence_proxy_async_smem();
+        tc_fence_after();
+        for (int i = 0; i < nsub; ++i)
+          if (ntiles_sub[i] > 0) issue_s(i, 0);
+        if (lane == 0) tc_commit(bar_ke(0));
+        __syncwarp();
+      }
+    }
+    for (int j = 0; j < ntiles && alive; ++j) {
+      const int s = j % kTcStages;
+      const uint32_t par = (j / kTcStages) & 1;
+      const int s1 = (j + 1) % kTcStages;
+      const uint32_t par1 = ((j + 1) / kTcStages) & 1;
+      alive = mbar_wait_warp(bar_vf(s), par, abort_flag);
+      if (!alive) break;
+      bool k_next_ready = false;
+      for (int i = 0; i < nsub && alive; ++i) {
+        if (j < ntiles_sub[i]) {
+          alive = mbar_wait_warp(bar_pf(i), j & 1, abort_flag);
+          if (!alive) break;
+          fence_proxy_async_smem();
+          tc_fence_after();
+          issue_pv(i, s, j == 0);
+        }
+        if (j + 1 < ntiles_sub[i]) {
+          if (!k_next_ready) {
+            alive = mbar_wait_warp(bar_kf(s1), par1, abort_flag);
+            if (!alive) break;
+            fence_proxy_async_smem();
+            tc_fence_after();
+            k_next_ready = true;
+          }
+          issue_s(i, s1);
+        }
+      }
+      if (!alive) break;
+      if (lane == 0) {
+        tc_commit(bar_ve(s));
+        if (j + 1 < ntiles) tc_commit(bar_ke(s1));
+      }
+      __syncwarp();
+    }
+    if (!alive && p.status && lane == 0) atomicExch(p.status, 1);
+  } else {
+    // =========================================================== softmax groups
+    const int i = warp >> 2;                 // sub-tile
+    const int r = tid & 127;                 // row inside the sub-tile == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_tm = tmem + lane_base + i * 128;
+    const uint32_t o_tm = tmem + lane_base + 256 + i * 128;
+    const int row = i * SUB + r;
+    const int pk = pk0 + row;
+    const int tl = pk / G, g = pk - tl * G;
+    const bool valid = row < rows_valid;
+    const int pos = sq.prefix + tl;
+    const int vhi = min(p.is_cross ? sq.L - 1 : min(pos, sq.L - 1), s_hi - 1);
+    const int vlo = max(p.window > 0 ? pos - p.window + 1 : 0, s_lo);
+    const int my_tiles = ntiles_sub[i];
+    float m_ref = -INFINITY, l = 0.f;
+    bool alive = true;
+
+    for (int j = 0; j < my_tiles; ++j) {
+      alive = mbar_wait_warp(bar_sf(i), j & 1, abort_flag);
+      if (!alive) break;
+      tc_fence_after();
+      const int k0 = kv_lo + j * BN;
+      const bool need_mask = !(k0 >= vlo && k0 + BN - 1 <= vhi);
+      // ---- pass 1: row maximum of the raw scores
+      float mt = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_tm + c * 32, v);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kpos = k0 + c * 32 + e;
+            if (kpos >= vlo && kpos <= vhi) mt = fmaxf(mt, __uint_as_float(v[e]) * p.scale_log2);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mt = fmaxf(mt, __uint_as_float(v[e]) * p.scale_log2);
+        }
+      }
+      // ---- lazy rescale of the accumulator
+      float alpha = 1.f;
+      bool resc = false;
+      if (mt > m_ref + 8.f) {
+        if (m_ref != -INFINITY) {
+          alpha = fast_exp2(m_ref - mt);
+          resc = true;
+        }
+        m_ref = mt;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, resc)) {
+        alive = mbar_wait_warp(bar_pv(i), (j - 1) & 1, abort_flag);
+        if (!alive) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(o_tm + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+          tmem_st32(o_tm + c * 32, v);
+        }
+        tmem_wait_st();
+      }
+      l *= alpha;
+      const float mu = (m_ref == -INFINITY) ? 0.f : m_ref;
+      // ---- pass 2: P = exp2(s*scale - m_ref) as packed 16-bit pairs over the S columns
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_tm + c * 32, v);
+        tmem_wait_ld();
+        uint32_t pk16[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float x0 = fmaf(__uint_as_float(v[e]), p.scale_log2, -mu);
+          float x1 = fmaf(__uint_as_float(v[e + 1]), p.scale_log2, -mu);
+          if (need_mask) {
+            const int kpos = k0 + c * 32 + e;
+            if (!(kpos >= vlo && kpos <= vhi)) x0 = -INFINITY;
+            if (!(kpos + 1 >= vlo && kpos + 1 <= vhi)) x1 = -INFINITY;
+          }
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          l += p0 + p1;
+          pk16[e >> 1] = MmaOp<T>::pack(p0, p1);
+        }
+        tmem_st16(s_tm + c * 16, pk16);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_pf(i));
+    }
+
+    // ---- epilogue
+    if (alive && my_tiles > 0) {
+      alive = mbar_wait_warp(bar_pv(i), (my_tiles - 1) & 1, abort_flag);
+      if (alive) tc_fence_after();
+    }
+    if (alive) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      if (p.kv_chunk == 0) {
+        T* orow = static_cast<T*>(p.out) +
+                  (static_cast<int64_t>(sq.q_begin + tl) * p.hq + static_cast<int64_t>(h) * G + g) * HD;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          if (my_tiles > 0) {
+            tmem_ld32(o_tm + c * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (valid) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 w;
+              w.x = MmaOp<T>::pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
+              w.y = MmaOp<T>::pack(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+              w.z = MmaOp<T>::pack(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
+              w.w = MmaOp<T>::pack(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
+            }
+          }
+        }
+      } else {
+        // unnormalised partial of this kv split (empty split: max = -inf, sum = 0)
+        const int64_t slot = static_cast<int64_t>(item) * p.hkv + h;
+        float* po = p.part_o + (slot * BM + row) * HD;
+        if (valid) {
+          *reinterpret_cast<float2*>(p.part_ml + (slot * BM + row) * 2) =
+              make_float2(my_tiles > 0 ? m_ref : -INFINITY, my_tiles > 0 ? l : 0.f);
+        }
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          if (my_tiles > 0) {
+            tmem_ld32(o_tm + c * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (valid) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<uint4*>(po + c * 32 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+          }
+        }
+      }
+    }
+    if (!alive && p.status && r == 0) atomicExch(p.status, 1);
+  }
+
+  // ---- teardown: every role is past its last TMEM access
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace msgl
