@@ -64,7 +64,11 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
   PrefillPlan pl{};
   const int G = hq / hkv;
   const int BM = msgl::kTcBM;
-  const int64_t qtiles = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, 0);
+  int64_t qtiles = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, 0);
+  {  // the other upper bound on the number of query tiles: every sequence at the longest length
+    const int64_t per_seq = (static_cast<int64_t>(max_len_extend) * G + BM - 1) / BM;
+    if (per_seq * batch < qtiles) qtiles = per_seq * batch;
+  }
   int64_t visible = total_kv;
   if (window > 0) {
     const int64_t w = static_cast<int64_t>(batch) * (static_cast<int64_t>(window) + max_len_extend);

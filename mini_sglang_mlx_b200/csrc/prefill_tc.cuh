@@ -4,11 +4,13 @@
 // One CTA owns 256 GQA-packed query rows of one KV head (two sub-tiles of 128
 // rows) and walks the visible key range in tiles of 128 tokens.
 //
-//   warps 0-3   softmax group 0: thread r owns row r of sub-tile 0 (TMEM lane r)
-//   warps 4-7   softmax group 1: the same for sub-tile 1
-//   warp  8     MMA issuer (one lane issues every tcgen05.mma / commit)
-//   warps 9-12  producers: gather Q rows and paged K/V token rows with 16-byte
-//               cp.async into 128-byte-swizzled shared-memory tiles
+//   warps 0-3    softmax group 0: thread r owns row r of sub-tile 0 (TMEM lane r)
+//   warps 4-7    softmax group 1: the same for sub-tile 1
+//   warp  8      MMA issuer (one lane issues every tcgen05.mma / commit); 9-11 idle
+//   warps 12-15  producers: gather Q rows and paged K/V token rows with 16-byte
+//                cp.async into 128-byte-swizzled shared-memory tiles
+// The softmax warps raise their register budget (setmaxnreg) so that a thread
+// can hold a whole 128-column score row; the other warps lower theirs.
 //
 // Per key tile j and sub-tile i:  S_i = Q_i K_j^T  (SS MMA, fp32 in TMEM)
 //   -> softmax group i reads S_i (tcgen05.ld), applies the mask on boundary
@@ -37,10 +39,11 @@ namespace msgl {
 constexpr int kTcBM = 256;        // packed query rows per CTA
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
 constexpr int kTcBN = 128;        // key tokens per tile
-constexpr int kTcStages = 2;      // K ring and V ring depth
-constexpr int kTcThreads = 13 * 32;
+constexpr int kTcBufs = 5;        // K/V ring: tile K_j uses buffer (2j)%5, V_j buffer (2j+1)%5
+constexpr int kTcThreads = 16 * 32;
+constexpr int kTcProducerWarp0 = 12;
 constexpr int kTcTileBytes = 128 * 256;                      // one 128-row x 128-element tile
-constexpr int kTcSmemBytes = (2 + 2 * kTcStages) * kTcTileBytes + 1024;  // + alignment slack
+constexpr int kTcSmemBytes = (2 + kTcBufs) * kTcTileBytes + 1024;  // + alignment slack
 constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -172,6 +175,45 @@ __device__ __forceinline__ void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+// Ties the registers written by an asynchronous tcgen05.ld to the wait that
+// precedes this call: no instruction, only a scheduling dependency.
+template <int N>
+__device__ __forceinline__ void reg_fence(uint32_t (&r)[N]) {
+#pragma unroll
+  for (int e = 0; e < N; ++e) asm volatile("" : "+r"(r[e])::"memory");
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 32 columns of this thread's TMEM lane into r[OFF .. OFF+32)
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_ld32_at(uint32_t taddr, uint32_t (&r)[N]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]),
+        "=r"(r[OFF + 5]), "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]),
+        "=r"(r[OFF + 10]), "=r"(r[OFF + 11]), "=r"(r[OFF + 12]), "=r"(r[OFF + 13]),
+        "=r"(r[OFF + 14]), "=r"(r[OFF + 15]), "=r"(r[OFF + 16]), "=r"(r[OFF + 17]),
+        "=r"(r[OFF + 18]), "=r"(r[OFF + 19]), "=r"(r[OFF + 20]), "=r"(r[OFF + 21]),
+        "=r"(r[OFF + 22]), "=r"(r[OFF + 23]), "=r"(r[OFF + 24]), "=r"(r[OFF + 25]),
+        "=r"(r[OFF + 26]), "=r"(r[OFF + 27]), "=r"(r[OFF + 28]), "=r"(r[OFF + 29]),
+        "=r"(r[OFF + 30]), "=r"(r[OFF + 31])
+      : "r"(taddr)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
 // lbo / sbo are byte offsets (leading / stride dimension).
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -201,8 +243,7 @@ __device__ __forceinline__ uint32_t tc_tile_offset(int row, int chunk) {
 
 struct TcBarriers {
   uint64_t q_full;
-  uint64_t k_full[kTcStages], k_empty[kTcStages];
-  uint64_t v_full[kTcStages], v_empty[kTcStages];
+  uint64_t full[kTcBufs], empty[kTcBufs];
   uint64_t s_full[2], p_full[2], pv_done[2];
 };
 
@@ -260,14 +301,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   // ---- shared-memory carve-up (1024-byte aligned tiles)
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem0;                                   // 2 sub-tiles
-  const uint32_t k_smem = smem0 + 2 * kTcTileBytes;                // kTcStages tiles
-  const uint32_t v_smem = k_smem + kTcStages * kTcTileBytes;       // kTcStages tiles
+  const uint32_t ring = smem0 + 2 * kTcTileBytes;                  // kTcBufs tiles
 
   const uint32_t bar_q = smem_u32(&bars.q_full);
-  auto bar_kf = [&](int s) { return smem_u32(&bars.k_full[s]); };
-  auto bar_ke = [&](int s) { return smem_u32(&bars.k_empty[s]); };
-  auto bar_vf = [&](int s) { return smem_u32(&bars.v_full[s]); };
-  auto bar_ve = [&](int s) { return smem_u32(&bars.v_empty[s]); };
+  auto bar_full = [&](int bf) { return smem_u32(&bars.full[bf]); };
+  auto bar_empty = [&](int bf) { return smem_u32(&bars.empty[bf]); };
   auto bar_sf = [&](int i) { return smem_u32(&bars.s_full[i]); };
   auto bar_pf = [&](int i) { return smem_u32(&bars.p_full[i]); };
   auto bar_pv = [&](int i) { return smem_u32(&bars.pv_done[i]); };
@@ -275,11 +313,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   if (tid == 0) {
     s_abort = 0;
     mbar_init(bar_q, NPROD);
-    for (int s = 0; s < kTcStages; ++s) {
-      mbar_init(bar_kf(s), NPROD);
-      mbar_init(bar_ke(s), 1);
-      mbar_init(bar_vf(s), NPROD);
-      mbar_init(bar_ve(s), 1);
+    for (int bf = 0; bf < kTcBufs; ++bf) {
+      mbar_init(bar_full(bf), NPROD);
+      mbar_init(bar_empty(bf), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_sf(i), 1);
@@ -298,9 +334,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   const uint32_t tmem = s_tmem_base;
   volatile int* abort_flag = &s_abort;
 
-  if (warp >= 9) {
+  if (warp >= kTcProducerWarp0) {
     // =========================================================== producers
-    const int ptid = tid - 9 * 32;         // 0..127
+    reg_dec<72>();
+    const int ptid = tid - kTcProducerWarp0 * 32;  // 0..127
     const int chunk = ptid & 15;           // 16-byte chunk of a 256-byte row
     const int rsub = ptid >> 4;            // 0..7: row inside a group of 8
     const T* __restrict__ q = static_cast<const T*>(p.q);
@@ -324,23 +361,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     }
     cp_async_mbar_arrive(bar_q);
 
-    int slots[16];
-    auto load_slots = [&](int tile) {
+    // slot ids of the 16 rows this thread copies in tile `tile` (-1: nothing to fetch).
+    // All 16 loads are issued before any is looked at, so they overlap.
+    auto load_slots = [&](int tile, int (&slots)[16]) {
+      const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int t = kv_lo + tile * BN + i * 8 + rsub;
-        int slot = -1;
-        if (tile < ntiles && t < kv_hi_load) {
-          slot = p.kv_indices[sq.kv_begin + t];
-          if (slot < 0 || static_cast<int64_t>(slot) >= p.num_slots) {
-            if (p.status) atomicExch(p.status, 2);
-            slot = -1;
-          }
-        }
-        slots[i] = slot;
+        slots[i] = (tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
       }
     };
-    auto issue = [&](uint32_t dst, const unsigned char* src_base) {
+    // out-of-range slot ids are reported once and treated as absent
+    auto check_slots = [&](int (&slots)[16]) {
+      bool bad = false;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const bool oob = slots[i] < -1 || static_cast<int64_t>(slots[i]) >= p.num_slots;
+        bad |= oob;
+        if (oob) slots[i] = -1;
+      }
+      if (bad && p.status) atomicExch(p.status, 2);
+    };
+    auto issue = [&](uint32_t dst, const unsigned char* src_base, const int (&slots)[16]) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int row = i * 8 + rsub;
@@ -350,33 +392,41 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
         cp_async_16(dst + tc_tile_offset(row, chunk), src_base + off, ok ? 16 : 0);
       }
     };
-    load_slots(0);
+    int cur[16], nxt[16];
+    load_slots(0, cur);
+    check_slots(cur);
     bool alive = true;
+#pragma unroll 1
     for (int j = 0; j < ntiles && alive; ++j) {
-      const int s = j % kTcStages;
-      const uint32_t par = ((j / kTcStages) & 1) ^ 1;
-      alive = mbar_wait_warp(bar_ke(s), par, abort_flag);
+      load_slots(j + 1, nxt);  // in flight while this tile's copies are issued
+      const int qk = 2 * j, qv = 2 * j + 1;
+      const int bk = qk % kTcBufs, bv = qv % kTcBufs;
+      alive = mbar_wait_warp(bar_empty(bk), ((qk / kTcBufs) & 1) ^ 1, abort_flag);
       if (!alive) break;
-      issue(k_smem + s * kTcTileBytes, kbase);
-      cp_async_mbar_arrive(bar_kf(s));
-      alive = mbar_wait_warp(bar_ve(s), par, abort_flag);
+      issue(ring + bk * kTcTileBytes, kbase, cur);
+      cp_async_mbar_arrive(bar_full(bk));
+      alive = mbar_wait_warp(bar_empty(bv), ((qv / kTcBufs) & 1) ^ 1, abort_flag);
       if (!alive) break;
-      issue(v_smem + s * kTcTileBytes, vbase);
-      cp_async_mbar_arrive(bar_vf(s));
-      load_slots(j + 1);
+      issue(ring + bv * kTcTileBytes, vbase, cur);
+      cp_async_mbar_arrive(bar_full(bv));
+#pragma unroll
+      for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
+      check_slots(cur);
     }
     cp_async_wait<0>();
     if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);
-  } else if (warp == 8) {
-    // =========================================================== MMA issuer
+  } else if (warp >= 8) {
+    // =========================================================== MMA issuer (warp 8)
+    reg_dec<72>();
+    if (warp == 8) {
     const uint32_t idesc_s = idesc_m128n128<T>(0);
     const uint32_t idesc_pv = idesc_m128n128<T>(1);
     bool alive = true;
-    auto issue_s = [&](int i, int stage) {
+    auto issue_s = [&](int i, int buf) {
       // S_i = Q_i K^T : 8 k-steps of 16 elements; both operands K-major
       if (lane == 0) {
         const uint32_t qa = q_smem + i * kTcTileBytes;
-        const uint32_t kb = k_smem + stage * kTcTileBytes;
+        const uint32_t kb = ring + buf * kTcTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t koff = (ks >> 2) * 16384 + (ks & 3) * 32;
@@ -387,10 +437,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       }
       __syncwarp();
     };
-    auto issue_pv = [&](int i, int stage, bool first) {
+    auto issue_pv = [&](int i, int buf, bool first) {
       // O_i (+)= P_i V : 8 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
       if (lane == 0) {
-        const uint32_t vb = v_smem + stage * kTcTileBytes;
+        const uint32_t vb = ring + buf * kTcTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           tc_mma_ts(tmem + 256 + i * 128, tmem + i * 128 + ks * 8,
@@ -402,22 +452,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       __syncwarp();
     };
     if (ntiles > 0) {
-      alive = mbar_wait_warp(bar_q, 0, abort_flag) && mbar_wait_warp(bar_kf(0), 0, abort_flag);
+      alive = mbar_wait_warp(bar_q, 0, abort_flag) && mbar_wait_warp(bar_full(0), 0, abort_flag);
       if (alive) {
         fence_proxy_async_smem();
         tc_fence_after();
         for (int i = 0; i < nsub; ++i)
           if (ntiles_sub[i] > 0) issue_s(i, 0);
-        if (lane == 0) tc_commit(bar_ke(0));
+        if (lane == 0) tc_commit(bar_empty(0));
         __syncwarp();
       }
     }
+#pragma unroll 1
     for (int j = 0; j < ntiles && alive; ++j) {
-      const int s = j % kTcStages;
-      const uint32_t par = (j / kTcStages) & 1;
-      const int s1 = (j + 1) % kTcStages;
-      const uint32_t par1 = ((j + 1) / kTcStages) & 1;
-      alive = mbar_wait_warp(bar_vf(s), par, abort_flag);
+      const int qv = 2 * j + 1, qk1 = 2 * j + 2;
+      const int bv = qv % kTcBufs, bk1 = qk1 % kTcBufs;
+      alive = mbar_wait_warp(bar_full(bv), (qv / kTcBufs) & 1, abort_flag);
       if (!alive) break;
       bool k_next_ready = false;
       for (int i = 0; i < nsub && alive; ++i) {
@@ -426,29 +475,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
           if (!alive) break;
           fence_proxy_async_smem();
           tc_fence_after();
-          issue_pv(i, s, j == 0);
+          issue_pv(i, bv, j == 0);
         }
         if (j + 1 < ntiles_sub[i]) {
           if (!k_next_ready) {
-            alive = mbar_wait_warp(bar_kf(s1), par1, abort_flag);
+            alive = mbar_wait_warp(bar_full(bk1), (qk1 / kTcBufs) & 1, abort_flag);
             if (!alive) break;
             fence_proxy_async_smem();
             tc_fence_after();
             k_next_ready = true;
           }
-          issue_s(i, s1);
+          issue_s(i, bk1);
         }
       }
       if (!alive) break;
       if (lane == 0) {
-        tc_commit(bar_ve(s));
-        if (j + 1 < ntiles) tc_commit(bar_ke(s1));
+        tc_commit(bar_empty(bv));
+        if (j + 1 < ntiles) tc_commit(bar_empty(bk1));
       }
       __syncwarp();
     }
     if (!alive && p.status && lane == 0) atomicExch(p.status, 1);
+    }
   } else {
     // =========================================================== softmax groups
+    reg_inc<184>();
     const int i = warp >> 2;                 // sub-tile
     const int r = tid & 127;                 // row inside the sub-tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -464,31 +515,40 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     const int my_tiles = ntiles_sub[i];
     float m_ref = -INFINITY, l = 0.f;
     bool alive = true;
+    const bool sc_neg = !(p.scale_log2 > 0.f);
+    const float sc = sc_neg ? 1.f : p.scale_log2;
 
+#pragma unroll 1
     for (int j = 0; j < my_tiles; ++j) {
       alive = mbar_wait_warp(bar_sf(i), j & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
       const int k0 = kv_lo + j * BN;
       const bool need_mask = !(k0 >= vlo && k0 + BN - 1 <= vhi);
-      // ---- pass 1: row maximum of the raw scores
-      float mt = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tm + c * 32, v);
-        tmem_wait_ld();
-        if (need_mask) {
+      // ---- the whole score row of this tile into registers
+      uint32_t v[128];
+      tmem_ld32_at<0>(s_tm, v);
+      tmem_ld32_at<32>(s_tm + 32, v);
+      tmem_ld32_at<64>(s_tm + 64, v);
+      tmem_ld32_at<96>(s_tm + 96, v);
+      tmem_wait_ld();
+      reg_fence(v);
+      if (sc_neg) {  // a non-positive scale: fold it into the scores so that max() commutes
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int kpos = k0 + c * 32 + e;
-            if (kpos >= vlo && kpos <= vhi) mt = fmaxf(mt, __uint_as_float(v[e]) * p.scale_log2);
-          }
-        } else {
+        for (int e = 0; e < 128; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * p.scale_log2);
+      }
+      if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mt = fmaxf(mt, __uint_as_float(v[e]) * p.scale_log2);
+        for (int e = 0; e < 128; ++e) {
+          const int kpos = k0 + e;
+          if (!(kpos >= vlo && kpos <= vhi)) v[e] = 0xff800000u;  // -inf
         }
       }
+      float mt = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 128; e += 2)
+        mt = max3(mt, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+      mt *= sc;
       // ---- lazy rescale of the accumulator
       float alpha = 1.f;
       bool resc = false;
@@ -505,39 +565,34 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(o_tm + c * 32, v);
+          uint32_t o[32];
+          tmem_ld32(o_tm + c * 32, o);
           tmem_wait_ld();
+          reg_fence(o);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-          tmem_st32(o_tm + c * 32, v);
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st32(o_tm + c * 32, o);
         }
         tmem_wait_st();
       }
       l *= alpha;
-      const float mu = (m_ref == -INFINITY) ? 0.f : m_ref;
-      // ---- pass 2: P = exp2(s*scale - m_ref) as packed 16-bit pairs over the S columns
-#pragma unroll 1
+      const float nmu = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      // ---- P = exp2(s*scale - m_ref) as packed 16-bit pairs over the S columns
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tm + c * 32, v);
-        tmem_wait_ld();
         uint32_t pk16[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float x0 = fmaf(__uint_as_float(v[e]), p.scale_log2, -mu);
-          float x1 = fmaf(__uint_as_float(v[e + 1]), p.scale_log2, -mu);
-          if (need_mask) {
-            const int kpos = k0 + c * 32 + e;
-            if (!(kpos >= vlo && kpos <= vhi)) x0 = -INFINITY;
-            if (!(kpos + 1 >= vlo && kpos + 1 <= vhi)) x1 = -INFINITY;
-          }
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-          l += p0 + p1;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e]), sc, nmu));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e + 1]), sc, nmu));
+          l0 += p0;
+          l1 += p1;
           pk16[e >> 1] = MmaOp<T>::pack(p0, p1);
         }
         tmem_st16(s_tm + c * 16, pk16);
       }
+      l += l0 + l1;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_pf(i));
@@ -559,6 +614,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
           if (my_tiles > 0) {
             tmem_ld32(o_tm + c * 32, v);
             tmem_wait_ld();
+            reg_fence(v);
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) v[e] = 0u;
@@ -589,6 +645,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
           if (my_tiles > 0) {
             tmem_ld32(o_tm + c * 32, v);
             tmem_wait_ld();
+            reg_fence(v);
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) v[e] = 0u;
