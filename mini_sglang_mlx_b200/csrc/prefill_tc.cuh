@@ -214,6 +214,18 @@ __device__ __forceinline__ void tmem_ld32_at(uint32_t taddr, uint32_t (&r)[N]) {
       : "memory");
 }
 
+// One lane of a converged warp (the same lane every time for a full mask).
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+      "elect.sync rx|px, %1;\n\t"
+      "@px mov.s32 %0, 1;\n\t}"
+      : "+r"(pred)
+      : "r"(0xFFFFFFFFu));
+  return pred;
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
 // lbo / sbo are byte offsets (leading / stride dimension).
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -422,32 +434,41 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     const uint32_t idesc_s = idesc_m128n128<T>(0);
     const uint32_t idesc_pv = idesc_m128n128<T>(1);
     bool alive = true;
+    // Descriptors are computed by the whole (converged) warp so that they stay
+    // warp-uniform values; only the elected lane issues the instructions.
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint64_t desc_hi_k = smem_desc_sw128(0, 16, 1024);      // Q / K: K-major
+    const uint64_t desc_hi_v = smem_desc_sw128(0, 16384, 1024);   // V: MN-major
     auto issue_s = [&](int i, int buf) {
       // S_i = Q_i K^T : 8 k-steps of 16 elements; both operands K-major
-      if (lane == 0) {
-        const uint32_t qa = q_smem + i * kTcTileBytes;
-        const uint32_t kb = ring + buf * kTcTileBytes;
+      const uint32_t qa = (q_smem + i * kTcTileBytes) >> 4;
+      const uint32_t kb = (ring + buf * kTcTileBytes) >> 4;
+      const uint32_t d_tm = tmem_u + i * 128;
+      const uint32_t bar = bar_sf(i);
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t koff = (ks >> 2) * 16384 + (ks & 3) * 32;
-          tc_mma_ss(tmem + i * 128, smem_desc_sw128(qa + koff, 16, 1024),
-                    smem_desc_sw128(kb + koff, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          const uint32_t koff = ((ks >> 2) * 16384 + (ks & 3) * 32) >> 4;
+          tc_mma_ss(d_tm, desc_hi_k | (qa + koff), desc_hi_k | (kb + koff), idesc_s,
+                    ks > 0 ? 1u : 0u);
         }
-        tc_commit(bar_sf(i));
+        tc_commit(bar);
       }
       __syncwarp();
     };
     auto issue_pv = [&](int i, int buf, bool first) {
       // O_i (+)= P_i V : 8 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
-      if (lane == 0) {
-        const uint32_t vb = ring + buf * kTcTileBytes;
+      const uint32_t vb = (ring + buf * kTcTileBytes) >> 4;
+      const uint32_t d_tm = tmem_u + 256 + i * 128;
+      const uint32_t a_tm = tmem_u + i * 128;
+      const uint32_t bar = bar_pv(i);
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          tc_mma_ts(tmem + 256 + i * 128, tmem + i * 128 + ks * 8,
-                    smem_desc_sw128(vb + ks * 2048, 16384, 1024), idesc_pv,
+          tc_mma_ts(d_tm, a_tm + ks * 8, desc_hi_v | (vb + ks * (2048 >> 4)), idesc_pv,
                     (first && ks == 0) ? 0u : 1u);
         }
-        tc_commit(bar_pv(i));
+        tc_commit(bar);
       }
       __syncwarp();
     };
@@ -458,7 +479,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
         tc_fence_after();
         for (int i = 0; i < nsub; ++i)
           if (ntiles_sub[i] > 0) issue_s(i, 0);
-        if (lane == 0) tc_commit(bar_empty(0));
+        if (elect_one()) tc_commit(bar_empty(0));
         __syncwarp();
       }
     }
@@ -489,7 +510,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
         }
       }
       if (!alive) break;
-      if (lane == 0) {
+      if (elect_one()) {
         tc_commit(bar_empty(bv));
         if (j + 1 < ntiles) tc_commit(bar_empty(bk1));
       }
