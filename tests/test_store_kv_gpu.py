@@ -61,12 +61,14 @@ class _Cfg:
     num_qo_heads = 8
 
 
-def _backend(num_pages=4096, rows=8, max_seq=2048, layers=2):
+def _backend(num_pages=16384, rows=8, max_seq=2048, layers=2):
     from mini_sglang_mlx_b200.attention import AttnBackend
     from mini_sglang_mlx_b200.kvcache import MHAKVCache
     pool = MHAKVCache(_Cfg.num_kv_heads, layers, _Cfg.head_dim, num_pages + 1, torch.bfloat16)
     g = torch.Generator().manual_seed(1)
-    table = torch.stack([torch.randperm(num_pages, generator=g)[:max_seq] for _ in range(rows)]).int().cuda()
+    # one permutation cut into rows: no slot belongs to two requests (a slot written twice in
+    # one scatter has no defined winner on a GPU)
+    table = torch.randperm(num_pages, generator=g)[: rows * max_seq].view(rows, max_seq).int().cuda()
     return AttnBackend(_Cfg, pool, table), pool, table
 
 
