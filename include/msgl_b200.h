@@ -86,6 +86,36 @@ int msgl_paged_decode_attention(
     int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t num_slots,
     int dtype, float sm_scale, int max_kv_splits, void* stream);
 
+/* Size of the scratch array built into the library for the entry point below. */
+#define MSGL_STATIC_SCRATCH_BYTES (32u << 20)
+
+/*
+ * Paged decode attention for callers that cannot allocate device memory.
+ * No counterpart in the reference: it exists for hosts that hold no allocator
+ * at the call site, for example a serving loop that runs inside a memory
+ * budget fixed at start-up, a plugin that is forbidden to call cudaMalloc
+ * because another runtime owns the device heap, or code running where an
+ * allocation would synchronise the device.  Same arguments and result as
+ * msgl_paged_decode_attention, minus the workspace: the split-KV partials go
+ * to a fixed array of MSGL_STATIC_SCRATCH_BYTES (32 MiB) inside the library,
+ * which every GPU that loads the library keeps until the process exits.
+ *  - Limit: msgl_decode_workspace_bytes(batch, num_q_heads, head_dim,
+ *    max_kv_splits) must not exceed MSGL_STATIC_SCRATCH_BYTES, i.e. about
+ *    batch * num_q_heads * max_kv_splits <= 65 000 at head_dim 128; larger
+ *    problems are rejected with MSGL_BAD_ARG and a message giving both sizes.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call
+ *    outside any stream capture.  No call allocates or frees memory.
+ *  - All calls on a device share the one array and it keeps the previous
+ *    call's contents; calls that overlap on the GPU (different streams) race
+ *    on it, so issue them on one stream or order them with events.
+ */
+int msgl_paged_decode_attention_static(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* num_kv_splits,
+    void* out, int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t num_slots,
+    int dtype, float sm_scale, int max_kv_splits, void* stream);
+
 /*
  * Bytes of scratch the prefill op needs for the given problem (split-KV
  * partials when there are too few query tiles to fill the GPU, plus a small

@@ -15,6 +15,7 @@ MSGL_OK = 0
 DTYPE_BF16 = 0
 DTYPE_F16 = 1
 MAX_KV_SPLITS_LIMIT = 128
+STATIC_SCRATCH_BYTES = 32 << 20
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
@@ -26,6 +27,8 @@ SIGNATURES = {
     "msgl_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "msgl_paged_decode_attention": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i64, _i, _f, _i, _vp]),
+    "msgl_paged_decode_attention_static": (
+        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _f, _i, _vp]),
     "msgl_prefill_workspace_bytes": (_sz, [_i, _i, _i64, _i, _i, _i, _i, _i]),
     "msgl_paged_prefill_attention": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i64, _i, _i, _i, _i64,

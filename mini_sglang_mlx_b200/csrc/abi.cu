@@ -5,6 +5,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 
 #include "../../include/msgl_b200.h"
@@ -26,6 +27,36 @@ int cuda_fail(const char* op, cudaError_t e) {
 }
 
 constexpr size_t kStatusBytes = 256;  // head of every workspace: device status word
+
+// Scratch of msgl_paged_decode_attention_static: lives in the library's image,
+// so every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_decode_scratch[MSGL_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
+
+// Device address of the static scratch on the current device.  In host code the
+// array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail("paged_decode_attention_static", e);
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(MSGL_BAD_ARG, "paged_decode_attention_static: device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_decode_scratch);
+    if (e != cudaSuccess) return cuda_fail("paged_decode_attention_static", e);
+    if (ptr == nullptr)
+      return fail(MSGL_CUDA_ERROR, "paged_decode_attention_static: no device address for the scratch");
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return MSGL_OK;
+}
 
 constexpr int kDecWarps = 4;
 constexpr int kDecStages = 3;
@@ -216,6 +247,36 @@ int msgl_paged_decode_attention(const void* q, const void* k_cache, const void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == MSGL_DTYPE_BF16) return launch_decode<__nv_bfloat16>(p, head_dim, s);
   return launch_decode<__half>(p, head_dim, s);
+}
+
+int msgl_paged_decode_attention_static(const void* q, const void* k_cache, const void* v_cache,
+                                       const int32_t* kv_indptr, const int32_t* kv_indices,
+                                       const int32_t* num_kv_splits, void* out, int batch,
+                                       int num_q_heads, int num_kv_heads, int head_dim,
+                                       int64_t num_slots, int dtype, float sm_scale,
+                                       int max_kv_splits, void* stream) {
+  // Size check first: it needs no device and must fail clearly.
+  if (batch > 0 && num_q_heads > 0 && head_dim > 0 && max_kv_splits > 0) {
+    const size_t need = msgl_decode_workspace_bytes(batch, num_q_heads, head_dim, max_kv_splits);
+    if (need > static_cast<size_t>(MSGL_STATIC_SCRATCH_BYTES))
+      return fail(MSGL_BAD_ARG,
+                  "paged_decode_attention_static: needs " + std::to_string(need) +
+                      " bytes of scratch, the built-in array holds " +
+                      std::to_string(static_cast<size_t>(MSGL_STATIC_SCRATCH_BYTES)) +
+                      "; lower batch * num_q_heads * max_kv_splits or use "
+                      "msgl_paged_decode_attention with a caller-supplied workspace");
+  }
+  if (batch == 0) return MSGL_OK;
+  void* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != MSGL_OK) return rc;
+  // Nothing in the scratch has to start at zero: every partial and log-sum-exp that the
+  // merge pass reads is written by the partial pass of the same call, and the status word
+  // at its head is sticky by design (zero when the library is loaded).
+  return msgl_paged_decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, out,
+                                     scratch, MSGL_STATIC_SCRATCH_BYTES, batch, num_q_heads,
+                                     num_kv_heads, head_dim, num_slots, dtype, sm_scale,
+                                     max_kv_splits, stream);
 }
 
 size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, int num_q_heads,
