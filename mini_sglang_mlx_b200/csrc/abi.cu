@@ -10,7 +10,6 @@
 
 #include "../../include/msgl_b200.h"
 #include "decode_splitkv.cuh"
-#include "prefill_mma.cuh"
 #include "prefill_tc.cuh"
 
 namespace {

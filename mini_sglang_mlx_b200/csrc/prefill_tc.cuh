@@ -691,4 +691,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   }
 }
 
+// Combines the kv-split partials of one (query token, query head).
+// grid = (total_q, hq), block = HD threads.
+template <typename T, int HD, int BM>
+__global__ void __launch_bounds__(HD) prefill_merge_kernel(const PrefillParams p) {
+  const int tok = blockIdx.x;
+  const int hq = blockIdx.y;
+  // sequence of this token: last b with qo_indptr[b] <= tok
+  int lo = 0, hi = p.batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.qo_indptr[mid] <= tok) lo = mid; else hi = mid;
+  }
+  const int b = lo;
+  const int q_begin = p.qo_indptr[b];
+  if (tok < q_begin || tok >= p.qo_indptr[b + 1]) return;  // token not covered by any sequence
+  const int G = p.group;
+  const int h = hq / G, g = hq - h * G;
+  const int pk = (tok - q_begin) * G + g;
+  const int qt = pk / BM, r = pk - qt * BM;
+  const int base = p.plan[2 * b], nsplit = p.plan[2 * b + 1];
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) {
+    const int64_t slot = static_cast<int64_t>(base + qt * nsplit + s) * p.hkv + h;
+    M = fmaxf(M, p.part_ml[(slot * BM + r) * 2]);
+  }
+  float num = 0.f, den = 0.f;
+  if (M != -INFINITY) {
+    for (int s = 0; s < nsplit; ++s) {
+      const int64_t slot = static_cast<int64_t>(base + qt * nsplit + s) * p.hkv + h;
+      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + (slot * BM + r) * 2);
+      const float w = fast_exp2(ml.x - M);  // exp2(-inf) = 0 for empty splits
+      den += w * ml.y;
+      num += w * p.part_o[(slot * BM + r) * HD + d];
+    }
+  }
+  static_cast<T*>(p.out)[(static_cast<int64_t>(tok) * p.hq + hq) * HD + d] =
+      MmaOp<T>::from_float(den > 0.f ? num / den : 0.f);
+}
+
 }  // namespace msgl
