@@ -328,7 +328,7 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
   const size_t need = kStatusBytes + pl.plan_bytes + pl.part_ml_bytes + pl.part_o_bytes;
   if (!workspace || workspace_bytes < need)
     return fail(MSGL_BAD_ARG, std::string(op) + "workspace too small");
-  if (pl.items > 0x7fffffffLL || num_q_heads > 65535)
+  if (pl.items * num_kv_heads > 0x7fffffffLL || num_q_heads > 65535)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "problem too large for one launch");
 
   msgl::PrefillParams p{};
@@ -359,7 +359,7 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
   p.kv_chunk = pl.kv_chunk;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  dim3 grid(static_cast<unsigned>(pl.items), num_kv_heads);
+  dim3 grid(static_cast<unsigned>(pl.items * num_kv_heads));
   dim3 mgrid(total_q, num_q_heads);
   cudaError_t e;
   if (dtype == MSGL_DTYPE_BF16) {

@@ -2,32 +2,32 @@
 // cores: tcgen05.mma with accumulators in tensor memory (TMEM), sm_100a only.
 //
 // One CTA owns 256 GQA-packed query rows of one KV head (two sub-tiles of 128
-// rows) and walks the visible key range in tiles of 128 tokens.
+// rows) and walks the visible key range in tiles of 64 tokens.
 //
 //   warps 0-3    softmax group 0: thread r owns row r of sub-tile 0 (TMEM lane r)
 //   warps 4-7    softmax group 1: the same for sub-tile 1
-//   warp  8      MMA issuer (one lane issues every tcgen05.mma / commit); 9-11 idle
+//   warp  8      MMA issuer (one elected lane issues every tcgen05.mma / commit); 9-11 idle
 //   warps 12-15  producers: gather Q rows and paged K/V token rows with 16-byte
 //                cp.async into 128-byte-swizzled shared-memory tiles
-// The softmax warps raise their register budget (setmaxnreg) so that a thread
-// can hold a whole 128-column score row; the other warps lower theirs.
 //
-// Per key tile j and sub-tile i:  S_i = Q_i K_j^T  (SS MMA, fp32 in TMEM)
-//   -> softmax group i reads S_i (tcgen05.ld), applies the mask on boundary
-//      tiles, keeps a running reference max (O is rescaled lazily, only when
-//      the max grows by more than 2^8), writes P_i as bf16 over the S_i columns
-//      (tcgen05.st)
-//   -> O_i += P_i V_j  (TS MMA: A from TMEM, V as an MN-major shared operand).
-// The issue order PV0_j, S0_{j+1}, PV1_j, S1_{j+1} keeps the tensor pipe busy
-// on one sub-tile while the other is in softmax.  All hand-offs are mbarriers;
-// every wait is bounded and reports through the status word instead of
-// hanging.  TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512).
+// Per key tile j and sub-tile i:  S_i[j] = Q_i K_j^T  (SS MMA M128 N64, fp32 in TMEM)
+//   -> softmax group i reads its 64-column row (tcgen05.ld), masks boundary
+//      tiles, keeps a running reference max (O is rescaled lazily, only when the
+//      max grows by more than 2^8), writes P as 16-bit pairs over the first 32
+//      of those columns (tcgen05.st)
+//   -> O_i += P V_j  (TS MMA M128 N128: A from TMEM, V as an MN-major shared operand).
+// S is double-buffered per sub-tile: S_i[j+2] is issued right after PV_i[j], so
+// the score tile of the next key tile is ready before the softmax group asks
+// for it and the softmax groups run back to back while the tensor pipe works
+// on the other tiles.  All hand-offs are mbarriers; every wait is bounded and
+// reports through the status word instead of hanging.
+// TMEM columns: S_i[b] at 128 i + 64 b (b = j mod 2), O_i at 256 + 128 i.
 //
-// Shared-memory tile layout (Q sub-tile, K tile and V tile alike): two
-// 16 KB halves, half h holding elements [64h, 64h+64) of every row; inside a
-// half row r sits at (r/8)*1024 + (r%8)*128 and its 16-byte chunk c at
-// position c ^ (r%8).  This is the canonical 128-byte-swizzle layout, K-major
-// for Q and K (rows = M/N index) and MN-major for V (rows = K index).
+// Shared-memory tile layout (Q sub-tile, K tile and V tile alike): two halves,
+// half h holding elements [64h, 64h+64) of every row; inside a half row r sits
+// at (r/8)*1024 + (r%8)*128 and its 16-byte chunk c at position c ^ (r%8).
+// This is the canonical 128-byte-swizzle layout, K-major for Q and K (rows =
+// M/N index) and MN-major for V (rows = K index).
 #pragma once
 
 #include <type_traits>
@@ -38,12 +38,13 @@ namespace msgl {
 
 constexpr int kTcBM = 256;        // packed query rows per CTA
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
-constexpr int kTcBN = 128;        // key tokens per tile
-constexpr int kTcBufs = 5;        // K/V ring: tile K_j uses buffer (2j)%5, V_j buffer (2j+1)%5
+constexpr int kTcBN = 64;         // key tokens per tile
+constexpr int kTcBufs = 9;        // K/V ring buffers (see ring_seq_k / ring_seq_v)
 constexpr int kTcThreads = 16 * 32;
 constexpr int kTcProducerWarp0 = 12;
-constexpr int kTcTileBytes = 128 * 256;                      // one 128-row x 128-element tile
-constexpr int kTcSmemBytes = (2 + kTcBufs) * kTcTileBytes + 1024;  // + alignment slack
+constexpr int kTcQTileBytes = 128 * 256;                     // one 128-row query sub-tile
+constexpr int kTcKvTileBytes = kTcBN * 256;                  // one 64-token K or V tile
+constexpr int kTcSmemBytes = 2 * kTcQTileBytes + kTcBufs * kTcKvTileBytes + 1024;  // + alignment slack
 constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -239,24 +240,34 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo,
 }
 
 // Instruction descriptor of kind::f16: fp32 accumulate, A/B both bf16 or both f16,
-// A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), M = 128, N = 128.
+// A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), M = 128, N = n.
 template <typename T>
-__device__ __forceinline__ uint32_t idesc_m128n128(uint32_t b_mn) {
+__device__ __forceinline__ uint32_t idesc_m128(uint32_t n, uint32_t b_mn) {
   const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((128u >> 3) << 17) |
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((n >> 3) << 17) |
          ((128u >> 4) << 24);
 }
 
-// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` (0..127) inside a tile.
+// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` inside a tile of ROWS rows.
+template <int ROWS>
 __device__ __forceinline__ uint32_t tc_tile_offset(int row, int chunk) {
-  return static_cast<uint32_t>(((chunk >> 3) << 14) + ((row >> 3) << 10) + ((row & 7) << 7) +
+  return static_cast<uint32_t>((chunk >> 3) * (ROWS * 128) + ((row >> 3) << 10) + ((row & 7) << 7) +
                                (((chunk & 7) ^ (row & 7)) << 4));
 }
+
+// Position of a tile in the order the MMA warp consumes the ring:
+// K0 K1 V0 K2 V1 K3 V2 ...  (S runs two key tiles ahead of PV).
+__device__ __forceinline__ int ring_seq_k(int j) { return j < 2 ? j : 2 * j - 1; }
+__device__ __forceinline__ int ring_seq_v(int j) { return 2 * j + 2; }
 
 struct TcBarriers {
   uint64_t q_full;
   uint64_t full[kTcBufs], empty[kTcBufs];
-  uint64_t s_full[2], p_full[2], pv_done[2];
+  // [sub-tile][S buffer]: a softmax group may finish tile j+1 before the MMA warp has
+  // looked at tile j, so both hand-offs are per S buffer (tiles j and j+2 never overlap)
+  // (with one PV barrier a group that waits only now and then could not tell completion
+  // j-2 from j by parity alone)
+  uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];
 };
 
 template <typename T>
@@ -272,19 +283,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.y;
+  const int h = static_cast<int>(blockIdx.x) % p.hkv;   // head fastest: a heavy item's heads start together
   const int G = p.group;
 
-  int b, local, base;
-  const int item = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-  if (!find_item<kTcThreads>(p, item, BM, b, local, base)) return;  // uniform for the block
-  const SeqShape sq = load_seq_shape(p, b, BM);
-  const int qt = local / sq.nsplit;
-  const int split = local % sq.nsplit;
-  if (p.plan && local == 0 && h == 0 && tid == 0) {
-    p.plan[2 * b] = base;
-    p.plan[2 * b + 1] = sq.nsplit;
+  ItemCoord it;
+  if (!find_item<kTcThreads>(p, static_cast<int>(blockIdx.x) / p.hkv, BM, it)) return;  // block-uniform
+  const SeqShape sq = load_seq_shape(p, it.b, BM);
+  const int qt = it.qt, split = it.split;
+  if (p.plan && it.first && h == 0 && tid == 0) {
+    p.plan[2 * it.b] = it.base;
+    p.plan[2 * it.b + 1] = sq.nsplit;
   }
+  const int slot_item = it.base + qt * sq.nsplit + split;   // where this item's kv-split partial goes
 
   // ---- geometry of the CTA's rows and of each sub-tile
   const int pk0 = qt * BM;
@@ -313,14 +323,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   // ---- shared-memory carve-up (1024-byte aligned tiles)
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem0;                                   // 2 sub-tiles
-  const uint32_t ring = smem0 + 2 * kTcTileBytes;                  // kTcBufs tiles
+  const uint32_t ring = smem0 + 2 * kTcQTileBytes;                 // kTcBufs K/V tiles
 
   const uint32_t bar_q = smem_u32(&bars.q_full);
   auto bar_full = [&](int bf) { return smem_u32(&bars.full[bf]); };
   auto bar_empty = [&](int bf) { return smem_u32(&bars.empty[bf]); };
-  auto bar_sf = [&](int i) { return smem_u32(&bars.s_full[i]); };
-  auto bar_pf = [&](int i) { return smem_u32(&bars.p_full[i]); };
-  auto bar_pv = [&](int i) { return smem_u32(&bars.pv_done[i]); };
+  auto bar_sf = [&](int i, int sb) { return smem_u32(&bars.s_full[i][sb]); };
+  auto bar_pf = [&](int i, int sb) { return smem_u32(&bars.p_full[i][sb]); };
+  auto bar_pv = [&](int i, int sb) { return smem_u32(&bars.pv_done[i][sb]); };
 
   if (tid == 0) {
     s_abort = 0;
@@ -330,9 +340,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       mbar_init(bar_empty(bf), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_sf(i), 1);
-      mbar_init(bar_pf(i), SUB);
-      mbar_init(bar_pv(i), 1);
+      mbar_init(bar_sf(i, 0), 1);
+      mbar_init(bar_sf(i, 1), 1);
+      mbar_init(bar_pf(i, 0), SUB);
+      mbar_init(bar_pf(i, 1), SUB);
+      mbar_init(bar_pv(i, 0), 1);
+      mbar_init(bar_pv(i, 1), 1);
     }
     fence_mbar_init();
   }
@@ -368,62 +381,77 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       const int64_t off =
           ok ? ((static_cast<int64_t>(sq.q_begin + tl) * p.hq + static_cast<int64_t>(h) * G + g) * HD)
              : 0;
-      cp_async_16(q_smem + (row >> 7) * kTcTileBytes + tc_tile_offset(row & 127, chunk),
+      cp_async_16(q_smem + (row >> 7) * kTcQTileBytes + tc_tile_offset<128>(row & 127, chunk),
                   reinterpret_cast<const unsigned char*>(q + off) + chunk * 16, ok ? 16 : 0);
     }
     cp_async_mbar_arrive(bar_q);
 
-    // slot ids of the 16 rows this thread copies in tile `tile` (-1: nothing to fetch).
-    // All 16 loads are issued before any is looked at, so they overlap.
-    auto load_slots = [&](int tile, int (&slots)[16]) {
+    constexpr int RPT = BN / 8;  // rows of a tile each producer thread copies
+    // slot ids of the rows this thread copies in tile `tile` (-1: nothing to fetch).
+    // All loads are issued before any is looked at, so they overlap.
+    auto load_slots = [&](int tile, int (&slots)[RPT]) {
       const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < RPT; ++i) {
         const int t = kv_lo + tile * BN + i * 8 + rsub;
         slots[i] = (tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
       }
     };
     // out-of-range slot ids are reported once and treated as absent
-    auto check_slots = [&](int (&slots)[16]) {
+    auto check_slots = [&](int (&slots)[RPT]) {
       bool bad = false;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < RPT; ++i) {
         const bool oob = slots[i] < -1 || static_cast<int64_t>(slots[i]) >= p.num_slots;
         bad |= oob;
         if (oob) slots[i] = -1;
       }
       if (bad && p.status) atomicExch(p.status, 2);
     };
-    auto issue = [&](uint32_t dst, const unsigned char* src_base, const int (&slots)[16]) {
+    auto issue = [&](uint32_t dst, const unsigned char* src_base, const int (&slots)[RPT]) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < RPT; ++i) {
         const int row = i * 8 + rsub;
         const bool ok = slots[i] >= 0;
         const int64_t off =
             (ok ? static_cast<int64_t>(slots[i]) * slot_stride + head_off : 0) + chunk * 16;
-        cp_async_16(dst + tc_tile_offset(row, chunk), src_base + off, ok ? 16 : 0);
+        cp_async_16(dst + tc_tile_offset<BN>(row, chunk), src_base + off, ok ? 16 : 0);
       }
     };
-    int cur[16], nxt[16];
-    load_slots(0, cur);
-    check_slots(cur);
     bool alive = true;
+    // copy one tile into the ring buffer of sequence number `seq`
+    auto produce = [&](int seq, const unsigned char* src_base, const int (&slots)[RPT]) {
+      const int bf = seq % kTcBufs;
+      alive = mbar_wait_warp(bar_empty(bf), ((seq / kTcBufs) & 1) ^ 1, abort_flag);
+      if (!alive) return;
+      issue(ring + bf * kTcKvTileBytes, src_base, slots);
+      cp_async_mbar_arrive(bar_full(bf));
+    };
+    int s0[RPT], s1[RPT], s2[RPT], s3[RPT];   // slot ids of tiles j, j+1, j+2 and (in flight) j+3
+    load_slots(0, s0);
+    load_slots(1, s1);
+    load_slots(2, s2);
+    check_slots(s0);
+    check_slots(s1);
+    check_slots(s2);
+    if (ntiles > 0) produce(ring_seq_k(0), kbase, s0);
+    if (ntiles > 1 && alive) produce(ring_seq_k(1), kbase, s1);
 #pragma unroll 1
     for (int j = 0; j < ntiles && alive; ++j) {
-      load_slots(j + 1, nxt);  // in flight while this tile's copies are issued
-      const int qk = 2 * j, qv = 2 * j + 1;
-      const int bk = qk % kTcBufs, bv = qv % kTcBufs;
-      alive = mbar_wait_warp(bar_empty(bk), ((qk / kTcBufs) & 1) ^ 1, abort_flag);
+      load_slots(j + 3, s3);  // in flight while this tile's copies are issued
+      produce(ring_seq_v(j), vbase, s0);
       if (!alive) break;
-      issue(ring + bk * kTcTileBytes, kbase, cur);
-      cp_async_mbar_arrive(bar_full(bk));
-      alive = mbar_wait_warp(bar_empty(bv), ((qv / kTcBufs) & 1) ^ 1, abort_flag);
-      if (!alive) break;
-      issue(ring + bv * kTcTileBytes, vbase, cur);
-      cp_async_mbar_arrive(bar_full(bv));
+      if (j + 2 < ntiles) {
+        produce(ring_seq_k(j + 2), kbase, s2);
+        if (!alive) break;
+      }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
-      check_slots(cur);
+      for (int i = 0; i < RPT; ++i) {
+        s0[i] = s1[i];
+        s1[i] = s2[i];
+        s2[i] = s3[i];
+      }
+      check_slots(s2);
     }
     cp_async_wait<0>();
     if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);
@@ -431,90 +459,94 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     // =========================================================== MMA issuer (warp 8)
     reg_dec<72>();
     if (warp == 8) {
-    const uint32_t idesc_s = idesc_m128n128<T>(0);
-    const uint32_t idesc_pv = idesc_m128n128<T>(1);
+    const uint32_t idesc_s = idesc_m128<T>(BN, 0);
+    const uint32_t idesc_pv = idesc_m128<T>(HD, 1);
     bool alive = true;
     // Descriptors are computed by the whole (converged) warp so that they stay
     // warp-uniform values; only the elected lane issues the instructions.
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
-    const uint64_t desc_hi_k = smem_desc_sw128(0, 16, 1024);      // Q / K: K-major
-    const uint64_t desc_hi_v = smem_desc_sw128(0, 16384, 1024);   // V: MN-major
-    auto issue_s = [&](int i, int buf) {
-      // S_i = Q_i K^T : 8 k-steps of 16 elements; both operands K-major
-      const uint32_t qa = (q_smem + i * kTcTileBytes) >> 4;
-      const uint32_t kb = (ring + buf * kTcTileBytes) >> 4;
-      const uint32_t d_tm = tmem_u + i * 128;
-      const uint32_t bar = bar_sf(i);
+    const uint64_t desc_hi_k = smem_desc_sw128(0, 16, 1024);                 // Q / K: K-major
+    const uint64_t desc_hi_v = smem_desc_sw128(0, BN * 128, 1024);           // V: MN-major
+    auto issue_s = [&](int i, int t, int buf) {
+      // S_i[t] = Q_i K_t^T : 8 k-steps of 16 elements; both operands K-major
+      const uint32_t qa = (q_smem + i * kTcQTileBytes) >> 4;
+      const uint32_t kb = (ring + buf * kTcKvTileBytes) >> 4;
+      const uint32_t d_tm = tmem_u + i * 128 + (t & 1) * BN;
+      const uint32_t bar = bar_sf(i, t & 1);
       if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t koff = ((ks >> 2) * 16384 + (ks & 3) * 32) >> 4;
-          tc_mma_ss(d_tm, desc_hi_k | (qa + koff), desc_hi_k | (kb + koff), idesc_s,
+          const uint32_t qoff = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;
+          const uint32_t koff = ((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4;
+          tc_mma_ss(d_tm, desc_hi_k | (qa + qoff), desc_hi_k | (kb + koff), idesc_s,
                     ks > 0 ? 1u : 0u);
         }
         tc_commit(bar);
       }
       __syncwarp();
     };
-    auto issue_pv = [&](int i, int buf, bool first) {
-      // O_i (+)= P_i V : 8 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
-      const uint32_t vb = (ring + buf * kTcTileBytes) >> 4;
+    auto issue_pv = [&](int i, int t, int buf) {
+      // O_i (+)= P V_t : 4 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
+      const uint32_t vb = (ring + buf * kTcKvTileBytes) >> 4;
       const uint32_t d_tm = tmem_u + 256 + i * 128;
-      const uint32_t a_tm = tmem_u + i * 128;
-      const uint32_t bar = bar_pv(i);
+      const uint32_t a_tm = tmem_u + i * 128 + (t & 1) * BN;
+      const uint32_t bar = bar_pv(i, t & 1);
       if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+        for (int ks = 0; ks < BN / 16; ++ks) {
           tc_mma_ts(d_tm, a_tm + ks * 8, desc_hi_v | (vb + ks * (2048 >> 4)), idesc_pv,
-                    (first && ks == 0) ? 0u : 1u);
+                    (t == 0 && ks == 0) ? 0u : 1u);
         }
         tc_commit(bar);
       }
       __syncwarp();
     };
-    if (ntiles > 0) {
-      alive = mbar_wait_warp(bar_q, 0, abort_flag) && mbar_wait_warp(bar_full(0), 0, abort_flag);
+    // wait for ring item `seq`, make its bytes visible to the tensor pipe
+    auto acquire = [&](int seq) {
+      alive = mbar_wait_warp(bar_full(seq % kTcBufs), (seq / kTcBufs) & 1, abort_flag);
       if (alive) {
         fence_proxy_async_smem();
         tc_fence_after();
+      }
+    };
+    auto release = [&](int seq) {
+      if (elect_one()) tc_commit(bar_empty(seq % kTcBufs));
+      __syncwarp();
+    };
+    if (ntiles > 0) {
+      alive = mbar_wait_warp(bar_q, 0, abort_flag);
+      for (int t = 0; t < 2 && t < ntiles && alive; ++t) {
+        acquire(ring_seq_k(t));
+        if (!alive) break;
         for (int i = 0; i < nsub; ++i)
-          if (ntiles_sub[i] > 0) issue_s(i, 0);
-        if (elect_one()) tc_commit(bar_empty(0));
-        __syncwarp();
+          if (t < ntiles_sub[i]) issue_s(i, t, ring_seq_k(t) % kTcBufs);
+        release(ring_seq_k(t));
       }
     }
 #pragma unroll 1
     for (int j = 0; j < ntiles && alive; ++j) {
-      const int qv = 2 * j + 1, qk1 = 2 * j + 2;
-      const int bv = qv % kTcBufs, bk1 = qk1 % kTcBufs;
-      alive = mbar_wait_warp(bar_full(bv), (qv / kTcBufs) & 1, abort_flag);
+      acquire(ring_seq_v(j));
       if (!alive) break;
-      bool k_next_ready = false;
+      bool k_ready = false;
       for (int i = 0; i < nsub && alive; ++i) {
         if (j < ntiles_sub[i]) {
-          alive = mbar_wait_warp(bar_pf(i), j & 1, abort_flag);
+          alive = mbar_wait_warp(bar_pf(i, j & 1), (j >> 1) & 1, abort_flag);
           if (!alive) break;
-          fence_proxy_async_smem();
           tc_fence_after();
-          issue_pv(i, bv, j == 0);
+          issue_pv(i, j, ring_seq_v(j) % kTcBufs);
         }
-        if (j + 1 < ntiles_sub[i]) {
-          if (!k_next_ready) {
-            alive = mbar_wait_warp(bar_full(bk1), (qk1 / kTcBufs) & 1, abort_flag);
+        if (j + 2 < ntiles_sub[i]) {
+          if (!k_ready) {
+            acquire(ring_seq_k(j + 2));
             if (!alive) break;
-            fence_proxy_async_smem();
-            tc_fence_after();
-            k_next_ready = true;
+            k_ready = true;
           }
-          issue_s(i, bk1);
+          issue_s(i, j + 2, ring_seq_k(j + 2) % kTcBufs);
         }
       }
       if (!alive) break;
-      if (elect_one()) {
-        tc_commit(bar_empty(bv));
-        if (j + 1 < ntiles) tc_commit(bar_empty(bk1));
-      }
-      __syncwarp();
+      release(ring_seq_v(j));
+      if (j + 2 < ntiles) release(ring_seq_k(j + 2));
     }
     if (!alive && p.status && lane == 0) atomicExch(p.status, 1);
     }
@@ -541,35 +573,37 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
 
 #pragma unroll 1
     for (int j = 0; j < my_tiles; ++j) {
-      alive = mbar_wait_warp(bar_sf(i), j & 1, abort_flag);
+      const int sb = j & 1;
+      alive = mbar_wait_warp(bar_sf(i, sb), (j >> 1) & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
       const int k0 = kv_lo + j * BN;
       const bool need_mask = !(k0 >= vlo && k0 + BN - 1 <= vhi);
-      // ---- the whole score row of this tile into registers
-      uint32_t v[128];
-      tmem_ld32_at<0>(s_tm, v);
-      tmem_ld32_at<32>(s_tm + 32, v);
-      tmem_ld32_at<64>(s_tm + 64, v);
-      tmem_ld32_at<96>(s_tm + 96, v);
+      // ---- the score row of this tile into registers
+      uint32_t v[BN];
+      tmem_ld32_at<0>(s_tm + sb * BN, v);
+      tmem_ld32_at<32>(s_tm + sb * BN + 32, v);
       tmem_wait_ld();
       reg_fence(v);
       if (sc_neg) {  // a non-positive scale: fold it into the scores so that max() commutes
 #pragma unroll
-        for (int e = 0; e < 128; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * p.scale_log2);
+        for (int e = 0; e < BN; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * p.scale_log2);
       }
       if (need_mask) {
 #pragma unroll
-        for (int e = 0; e < 128; ++e) {
+        for (int e = 0; e < BN; ++e) {
           const int kpos = k0 + e;
           if (!(kpos >= vlo && kpos <= vhi)) v[e] = 0xff800000u;  // -inf
         }
       }
-      float mt = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 128; e += 2)
-        mt = max3(mt, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
-      mt *= sc;
+      for (int e = 0; e < BN; e += 8) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          mx[c] = max3(mx[c], __uint_as_float(v[e + 2 * c]), __uint_as_float(v[e + 2 * c + 1]));
+      }
+      const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;
       // ---- lazy rescale of the accumulator
       float alpha = 1.f;
       bool resc = false;
@@ -581,7 +615,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
         m_ref = mt;
       }
       if (j > 0 && __any_sync(0xffffffffu, resc)) {
-        alive = mbar_wait_warp(bar_pv(i), (j - 1) & 1, abort_flag);
+        alive = mbar_wait_warp(bar_pv(i, (j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
@@ -601,7 +635,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       // ---- P = exp2(s*scale - m_ref) as packed 16-bit pairs over the S columns
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t pk16[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -611,17 +645,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
           l1 += p1;
           pk16[e >> 1] = MmaOp<T>::pack(p0, p1);
         }
-        tmem_st16(s_tm + c * 16, pk16);
+        tmem_st16(s_tm + sb * BN + c * 16, pk16);
       }
       l += l0 + l1;
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_pf(i));
+      mbar_arrive(bar_pf(i, sb));
     }
 
     // ---- epilogue
     if (alive && my_tiles > 0) {
-      alive = mbar_wait_warp(bar_pv(i), (my_tiles - 1) & 1, abort_flag);
+      alive = mbar_wait_warp(bar_pv(i, (my_tiles - 1) & 1), ((my_tiles - 1) >> 1) & 1, abort_flag);
       if (alive) tc_fence_after();
     }
     if (alive) {
@@ -654,7 +688,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
         }
       } else {
         // unnormalised partial of this kv split (empty split: max = -inf, sum = 0)
-        const int64_t slot = static_cast<int64_t>(item) * p.hkv + h;
+        const int64_t slot = static_cast<int64_t>(slot_item) * p.hkv + h;
         float* po = p.part_o + (slot * BM + row) * HD;
         if (valid) {
           *reinterpret_cast<float2*>(p.part_ml + (slot * BM + row) * 2) =

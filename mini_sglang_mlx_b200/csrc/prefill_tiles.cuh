@@ -4,9 +4,9 @@
 // pk = token_local * G + g addresses query token token_local and query head
 // kv_head * G + g, so that all G heads sharing a KV head sit in the same tile
 // and K/V is read once per KV head.  A tile is BM consecutive packed rows.
-// A work item is (sequence, q tile, kv split); items are numbered densely in
-// sequence order and a CTA finds its item from blockIdx.x with a block-wide
-// scan over the sequences' item counts (no planning launch, no host sync).
+// A work item is (sequence, q tile, kv split); items are numbered densely and a
+// CTA finds its item from its launch rank with a block-wide pass over the
+// sequences' item counts (no planning launch, no host sync).
 //
 // Mask semantics are those of the reference kernel
 // (mini-sglang-mlx-kernel/csrc/paged_prefill_attention.metal:324-350 and
@@ -60,56 +60,117 @@ __device__ __forceinline__ SeqShape load_seq_shape(const PrefillParams& p, int b
   return s;
 }
 
-// Block-wide search for the sequence that owns flat item id `item`.
-// Returns false (for the whole block) if item is past the last one.
-// On success: b = sequence, local = item index inside it, base = its first item.
+// Which (sequence, q tile, kv split) a CTA works on.
+struct ItemCoord {
+  int b, qt, split;
+  int base;    // id of the sequence's first item; an item's scratch slot is base + qt*nsplit + split
+  bool first;  // exactly one item per sequence has this set (it publishes the plan entry)
+};
+
+constexpr int kSortedBatchMax = 128;
+
+// Block-wide mapping from a launch rank (0 = scheduled first) to a work item.
+// Returns false (for the whole block) if the rank is past the last item.
+// Heavy items get low ranks so that the hardware's in-order CTA dispatch
+// approximates longest-first scheduling: with at most kSortedBatchMax sequences
+// they are ordered by visible key length, longest first, and inside a sequence
+// the last (causally longest) q tile comes first; larger batches keep the
+// natural order, reversed.
 template <int NTHREADS>
-__device__ __forceinline__ bool find_item(const PrefillParams& p, int item, int BM, int& b_out,
-                                          int& local_out, int& base_out) {
-  __shared__ int s_warp_tot[NTHREADS / 32];
-  __shared__ int s_found[3];
+__device__ __forceinline__ bool find_item(const PrefillParams& p, int rank, int BM, ItemCoord& out) {
+  __shared__ int s_res[5];
   const int tid = threadIdx.x;
-  const int lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) s_found[0] = -1;
-  __syncthreads();
-  int running = 0;
-  for (int b0 = 0; b0 < p.batch; b0 += NTHREADS) {
-    const int b = b0 + tid;
-    int items = 0;
-    if (b < p.batch) {
-      const SeqShape s = load_seq_shape(p, b, BM);
-      items = s.nqt * s.nsplit;
+  if (tid == 0) s_res[0] = -1;
+  if (p.batch <= kSortedBatchMax) {
+    __shared__ int s_key[kSortedBatchMax], s_cnt[kSortedBatchMax], s_nsplit[kSortedBatchMax];
+    __shared__ int s_ord[kSortedBatchMax];
+    if (tid < p.batch) {
+      const SeqShape s = load_seq_shape(p, tid, BM);
+      s_key[tid] = s.hi - s.lo;
+      s_cnt[tid] = s.nqt * s.nsplit;
+      s_nsplit[tid] = s.nsplit;
     }
-    int incl = items;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    if (lane == 31) s_warp_tot[warp] = incl;
     __syncthreads();
-    int warp_base = 0, total = 0;
-#pragma unroll
-    for (int w = 0; w < NTHREADS / 32; ++w) {
-      const int t = s_warp_tot[w];
-      if (w < warp) warp_base += t;
-      total += t;
+    if (tid < p.batch) {
+      const int key = s_key[tid];
+      int r = 0;
+      for (int k = 0; k < p.batch; ++k) {
+        const int kk = s_key[k];
+        r += (kk > key || (kk == key && k < tid)) ? 1 : 0;
+      }
+      s_ord[r] = tid;
     }
-    const int excl = running + warp_base + incl - items;
-    if (items > 0 && item >= excl && item < excl + items) {
-      s_found[0] = b;
-      s_found[1] = item - excl;
-      s_found[2] = excl;
-    }
-    running += total;
     __syncthreads();
-    if (running > item) break;
+    if (tid == 0) {
+      int running = 0;
+      for (int r = 0; r < p.batch; ++r) {
+        const int b = s_ord[r];
+        const int c = s_cnt[b];
+        if (rank < running + c) {
+          const int local = rank - running;
+          const int nsplit = s_nsplit[b];
+          s_res[0] = b;
+          s_res[1] = c / nsplit - 1 - local / nsplit;  // last q tile first
+          s_res[2] = local % nsplit;
+          s_res[3] = running;
+          s_res[4] = local == 0;
+          break;
+        }
+        running += c;
+      }
+    }
+    __syncthreads();
+  } else {
+    // natural order, reversed: item = (items launched) - 1 - rank
+    __shared__ int s_warp_tot[NTHREADS / 32];
+    const int item = static_cast<int>(gridDim.x) / p.hkv - 1 - rank;
+    const int lane = tid & 31, warp = tid >> 5;
+    __syncthreads();
+    int running = 0;
+    for (int b0 = 0; b0 < p.batch; b0 += NTHREADS) {
+      const int b = b0 + tid;
+      int items = 0, nsplit = 1;
+      if (b < p.batch) {
+        const SeqShape s = load_seq_shape(p, b, BM);
+        items = s.nqt * s.nsplit;
+        nsplit = s.nsplit;
+      }
+      int incl = items;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (lane == 31) s_warp_tot[warp] = incl;
+      __syncthreads();
+      int warp_base = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < NTHREADS / 32; ++w) {
+        const int t = s_warp_tot[w];
+        if (w < warp) warp_base += t;
+        total += t;
+      }
+      const int excl = running + warp_base + incl - items;
+      if (items > 0 && item >= excl && item < excl + items) {
+        const int local = item - excl;
+        s_res[0] = b;
+        s_res[1] = local / nsplit;
+        s_res[2] = local % nsplit;
+        s_res[3] = excl;
+        s_res[4] = local == 0;
+      }
+      running += total;
+      __syncthreads();
+      if (running > item) break;
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  b_out = s_found[0];
-  local_out = s_found[1];
-  base_out = s_found[2];
-  return b_out >= 0;
+  out.b = s_res[0];
+  out.qt = s_res[1];
+  out.split = s_res[2];
+  out.base = s_res[3];
+  out.first = s_res[4] != 0;
+  return out.b >= 0;
 }
 
 // Upper bound (host side) on the number of work items.
