@@ -361,22 +361,28 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
 
   dim3 grid(static_cast<unsigned>(pl.items * num_kv_heads));
   dim3 mgrid(total_q, num_q_heads);
+  // Query blocks that fill at most one 128-row sub-tile (verify, draft blocks) take the
+  // 64-token key tiles whose score tiles are double-buffered; longer chunks take 128-token
+  // tiles, which read Q from shared memory half as often.
+  const bool short_q = static_cast<int64_t>(max_len_extend) * p.group <= msgl::kTcSub;
   cudaError_t e;
+  auto launch = [&](auto kernel, auto merge) -> cudaError_t {
+    cudaError_t err = allow_smem(kernel, msgl::kTcSmemBytes);
+    if (err != cudaSuccess) return err;
+    kernel<<<grid, msgl::kTcThreads, msgl::kTcSmemBytes, s>>>(p);
+    if (pl.kv_chunk > 0) merge<<<mgrid, 128, 0, s>>>(p);
+    return cudaSuccess;
+  };
   if (dtype == MSGL_DTYPE_BF16) {
-    auto k = msgl::prefill_tc_kernel<__nv_bfloat16>;
-    if ((e = allow_smem(k, msgl::kTcSmemBytes)) != cudaSuccess)
-      return cuda_fail("paged_prefill_attention", e);
-    k<<<grid, msgl::kTcThreads, msgl::kTcSmemBytes, s>>>(p);
-    if (pl.kv_chunk > 0)
-      msgl::prefill_merge_kernel<__nv_bfloat16, 128, msgl::kTcBM><<<mgrid, 128, 0, s>>>(p);
+    using T = __nv_bfloat16;
+    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>)
+                : launch(msgl::prefill_tc_kernel<T, 128>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>);
   } else {
-    auto k = msgl::prefill_tc_kernel<__half>;
-    if ((e = allow_smem(k, msgl::kTcSmemBytes)) != cudaSuccess)
-      return cuda_fail("paged_prefill_attention", e);
-    k<<<grid, msgl::kTcThreads, msgl::kTcSmemBytes, s>>>(p);
-    if (pl.kv_chunk > 0)
-      msgl::prefill_merge_kernel<__half, 128, msgl::kTcBM><<<mgrid, 128, 0, s>>>(p);
+    using T = __half;
+    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>)
+                : launch(msgl::prefill_tc_kernel<T, 128>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>);
   }
+  if (e != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   return MSGL_OK;
 }

@@ -2,7 +2,10 @@
 // cores: tcgen05.mma with accumulators in tensor memory (TMEM), sm_100a only.
 //
 // One CTA owns 256 GQA-packed query rows of one KV head (two sub-tiles of 128
-// rows) and walks the visible key range in tiles of 64 tokens.
+// rows) and walks the visible key range in tiles of BN tokens.  Two variants:
+// BN = 128 (S single-buffered; the two sub-tiles ping-pong on the tensor pipe)
+// for long query chunks, BN = 64 (S double-buffered, S runs two key tiles
+// ahead of PV) for short query blocks where only one sub-tile has rows.
 //
 //   warps 0-3    softmax group 0: thread r owns row r of sub-tile 0 (TMEM lane r)
 //   warps 4-7    softmax group 1: the same for sub-tile 1
@@ -10,18 +13,16 @@
 //   warps 12-15  producers: gather Q rows and paged K/V token rows with 16-byte
 //                cp.async into 128-byte-swizzled shared-memory tiles
 //
-// Per key tile j and sub-tile i:  S_i[j] = Q_i K_j^T  (SS MMA M128 N64, fp32 in TMEM)
-//   -> softmax group i reads its 64-column row (tcgen05.ld), masks boundary
+// Per key tile j and sub-tile i:  S_i[j] = Q_i K_j^T  (SS MMA M128 N=BN, fp32 in TMEM)
+//   -> softmax group i reads its BN-column row (tcgen05.ld), masks boundary
 //      tiles, keeps a running reference max (O is rescaled lazily, only when the
-//      max grows by more than 2^8), writes P as 16-bit pairs over the first 32
+//      max grows by more than 2^8), writes P as 16-bit pairs over the first BN/2
 //      of those columns (tcgen05.st)
 //   -> O_i += P V_j  (TS MMA M128 N128: A from TMEM, V as an MN-major shared operand).
-// S is double-buffered per sub-tile: S_i[j+2] is issued right after PV_i[j], so
-// the score tile of the next key tile is ready before the softmax group asks
-// for it and the softmax groups run back to back while the tensor pipe works
-// on the other tiles.  All hand-offs are mbarriers; every wait is bounded and
-// reports through the status word instead of hanging.
-// TMEM columns: S_i[b] at 128 i + 64 b (b = j mod 2), O_i at 256 + 128 i.
+// S_i[j+LA] is issued right after PV_i[j] (LA = 1 for BN 128, 2 for BN 64 where
+// S has two buffers per sub-tile).  All hand-offs are mbarriers; every wait is
+// bounded and reports through the status word instead of hanging.
+// TMEM columns: S_i[b] at 128 i + BN b (b = j mod 2 if double-buffered), O_i at 256 + 128 i.
 //
 // Shared-memory tile layout (Q sub-tile, K tile and V tile alike): two halves,
 // half h holding elements [64h, 64h+64) of every row; inside a half row r sits
@@ -38,13 +39,11 @@ namespace msgl {
 
 constexpr int kTcBM = 256;        // packed query rows per CTA
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
-constexpr int kTcBN = 64;         // key tokens per tile
-constexpr int kTcBufs = 9;        // K/V ring buffers (see ring_seq_k / ring_seq_v)
+constexpr int kTcRingBytes = 5 * 128 * 256;  // K/V ring: 5 tiles of 128 tokens or 10 of 64
 constexpr int kTcThreads = 16 * 32;
 constexpr int kTcProducerWarp0 = 12;
 constexpr int kTcQTileBytes = 128 * 256;                     // one 128-row query sub-tile
-constexpr int kTcKvTileBytes = kTcBN * 256;                  // one 64-token K or V tile
-constexpr int kTcSmemBytes = 2 * kTcQTileBytes + kTcBufs * kTcKvTileBytes + 1024;  // + alignment slack
+constexpr int kTcSmemBytes = 2 * kTcQTileBytes + kTcRingBytes + 1024;  // + alignment slack
 constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -255,14 +254,17 @@ __device__ __forceinline__ uint32_t tc_tile_offset(int row, int chunk) {
                                (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// Position of a tile in the order the MMA warp consumes the ring:
-// K0 K1 V0 K2 V1 K3 V2 ...  (S runs two key tiles ahead of PV).
-__device__ __forceinline__ int ring_seq_k(int j) { return j < 2 ? j : 2 * j - 1; }
-__device__ __forceinline__ int ring_seq_v(int j) { return 2 * j + 2; }
+// Position of a tile in the order the MMA warp consumes the ring when S runs LA
+// key tiles ahead of PV:  K_0 .. K_{LA-1}, then V_0 K_LA V_1 K_{LA+1} ...
+template <int LA>
+__device__ __forceinline__ int ring_seq_k(int t) { return t < LA ? t : 2 * t - LA + 1; }
+template <int LA>
+__device__ __forceinline__ int ring_seq_v(int j) { return 2 * j + LA; }
 
 struct TcBarriers {
   uint64_t q_full;
-  uint64_t full[kTcBufs], empty[kTcBufs];
+  uint64_t idx_sync;  // producers only: guards the staged slot ids
+  uint64_t full[10], empty[10];
   // [sub-tile][S buffer]: a softmax group may finish tile j+1 before the MMA warp has
   // looked at tile j, so both hand-offs are per S buffer (tiles j and j+2 never overlap)
   // (with one PV barrier a group that waits only now and then could not tell completion
@@ -270,27 +272,33 @@ struct TcBarriers {
   uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];
 };
 
-template <typename T>
+template <typename T, int BN>
 __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const PrefillParams p) {
+  static_assert(BN == 64 || BN == 128, "key tile of 64 or 128 tokens");
   constexpr int HD = 128;
-  constexpr int BM = kTcBM, SUB = kTcSub, BN = kTcBN;
+  constexpr int BM = kTcBM, SUB = kTcSub;
   constexpr int NPROD = 128;  // producer threads
+  constexpr int LA = BN == 64 ? 2 : 1;        // key tiles S runs ahead of PV (= S buffers per sub-tile)
+  constexpr int kTcKvTileBytes = BN * 256;
+  constexpr int kTcBufs = kTcRingBytes / kTcKvTileBytes;
 
-  extern __shared__ unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ TcBarriers bars;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ int s_slots[(LA + 1) * BN];  // slot ids of the key tiles being copied / next to copy
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int h = static_cast<int>(blockIdx.x) % p.hkv;   // head fastest: a heavy item's heads start together
   const int G = p.group;
 
   ItemCoord it;
-  if (!find_item<kTcThreads>(p, static_cast<int>(blockIdx.x) / p.hkv, BM, it)) return;  // block-uniform
+  if (!find_item<kTcThreads>(p, static_cast<int>(blockIdx.x), BM, reinterpret_cast<int*>(smem_raw), it))
+    return;  // block-uniform
+  const int h = it.h;
   const SeqShape sq = load_seq_shape(p, it.b, BM);
   const int qt = it.qt, split = it.split;
-  if (p.plan && it.first && h == 0 && tid == 0) {
+  if (p.plan && it.first && tid == 0) {
     p.plan[2 * it.b] = it.base;
     p.plan[2 * it.b + 1] = sq.nsplit;
   }
@@ -335,6 +343,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   if (tid == 0) {
     s_abort = 0;
     mbar_init(bar_q, NPROD);
+    mbar_init(smem_u32(&bars.idx_sync), NPROD);
     for (int bf = 0; bf < kTcBufs; ++bf) {
       mbar_init(bar_full(bf), NPROD);
       mbar_init(bar_empty(bf), 1);
@@ -361,7 +370,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
 
   if (warp >= kTcProducerWarp0) {
     // =========================================================== producers
-    reg_dec<72>();
+    reg_dec<56>();
     const int ptid = tid - kTcProducerWarp0 * 32;  // 0..127
     const int chunk = ptid & 15;           // 16-byte chunk of a 256-byte row
     const int rsub = ptid >> 4;            // 0..7: row inside a group of 8
@@ -387,77 +396,72 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     cp_async_mbar_arrive(bar_q);
 
     constexpr int RPT = BN / 8;  // rows of a tile each producer thread copies
-    // slot ids of the rows this thread copies in tile `tile` (-1: nothing to fetch).
-    // All loads are issued before any is looked at, so they overlap.
-    auto load_slots = [&](int tile, int (&slots)[RPT]) {
-      const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
-#pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int t = kv_lo + tile * BN + i * 8 + rsub;
-        slots[i] = (tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
-      }
+    // Slot ids are staged in shared memory: thread r fetches the id of row r of a tile (one
+    // coalesced load per tile, two tiles ahead of its use), out-of-range ids are reported
+    // once and stored as -1 (row treated as absent).  Tile t lives in s_slots[(t % (LA+1)) * BN ..].
+    const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
+    auto fetch_slot = [&](int tile) -> int {
+      const int t = kv_lo + tile * BN + ptid;
+      return (ptid < BN && tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
     };
-    // out-of-range slot ids are reported once and treated as absent
-    auto check_slots = [&](int (&slots)[RPT]) {
-      bool bad = false;
-#pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const bool oob = slots[i] < -1 || static_cast<int64_t>(slots[i]) >= p.num_slots;
-        bad |= oob;
-        if (oob) slots[i] = -1;
-      }
-      if (bad && p.status) atomicExch(p.status, 2);
-    };
-    auto issue = [&](uint32_t dst, const unsigned char* src_base, const int (&slots)[RPT]) {
-#pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int row = i * 8 + rsub;
-        const bool ok = slots[i] >= 0;
-        const int64_t off =
-            (ok ? static_cast<int64_t>(slots[i]) * slot_stride + head_off : 0) + chunk * 16;
-        cp_async_16(dst + tc_tile_offset<BN>(row, chunk), src_base + off, ok ? 16 : 0);
+    auto stage_slot = [&](int tile, int slot) {
+      if (ptid < BN) {
+        if (slot < -1 || static_cast<int64_t>(slot) >= p.num_slots) {
+          if (p.status) atomicExch(p.status, 2);
+          slot = -1;
+        }
+        s_slots[(tile % (LA + 1)) * BN + ptid] = slot;
       }
     };
     bool alive = true;
+    uint32_t idx_phase = 0;
+    const uint32_t bar_idx = smem_u32(&bars.idx_sync);
+    auto producers_sync = [&]() {  // bounded barrier among the 128 producer threads
+      mbar_arrive(bar_idx);
+      alive = mbar_wait_warp(bar_idx, idx_phase, abort_flag);
+      idx_phase ^= 1;
+    };
     // copy one tile into the ring buffer of sequence number `seq`
-    auto produce = [&](int seq, const unsigned char* src_base, const int (&slots)[RPT]) {
+    auto produce = [&](int seq, const unsigned char* src_base, int tile) {
       const int bf = seq % kTcBufs;
       alive = mbar_wait_warp(bar_empty(bf), ((seq / kTcBufs) & 1) ^ 1, abort_flag);
       if (!alive) return;
-      issue(ring + bf * kTcKvTileBytes, src_base, slots);
-      cp_async_mbar_arrive(bar_full(bf));
-    };
-    int s0[RPT], s1[RPT], s2[RPT], s3[RPT];   // slot ids of tiles j, j+1, j+2 and (in flight) j+3
-    load_slots(0, s0);
-    load_slots(1, s1);
-    load_slots(2, s2);
-    check_slots(s0);
-    check_slots(s1);
-    check_slots(s2);
-    if (ntiles > 0) produce(ring_seq_k(0), kbase, s0);
-    if (ntiles > 1 && alive) produce(ring_seq_k(1), kbase, s1);
-#pragma unroll 1
-    for (int j = 0; j < ntiles && alive; ++j) {
-      load_slots(j + 3, s3);  // in flight while this tile's copies are issued
-      produce(ring_seq_v(j), vbase, s0);
-      if (!alive) break;
-      if (j + 2 < ntiles) {
-        produce(ring_seq_k(j + 2), kbase, s2);
-        if (!alive) break;
-      }
+      const uint32_t dst = ring + bf * kTcKvTileBytes;
+      const int* slots = s_slots + (tile % (LA + 1)) * BN;
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
-        s0[i] = s1[i];
-        s1[i] = s2[i];
-        s2[i] = s3[i];
+        const int row = i * 8 + rsub;
+        const int slot = slots[row];
+        const bool ok = slot >= 0;
+        const int64_t off =
+            (ok ? static_cast<int64_t>(slot) * slot_stride + head_off : 0) + chunk * 16;
+        cp_async_16(dst + tc_tile_offset<BN>(row, chunk), src_base + off, ok ? 16 : 0);
       }
-      check_slots(s2);
+      cp_async_mbar_arrive(bar_full(bf));
+    };
+#pragma unroll
+    for (int t = 0; t <= LA; ++t) stage_slot(t, fetch_slot(t));
+    producers_sync();
+    for (int t = 0; t < LA && t < ntiles && alive; ++t) produce(ring_seq_k<LA>(t), kbase, t);
+#pragma unroll 1
+    for (int j = 0; j < ntiles && alive; ++j) {
+      const int next_slot = fetch_slot(j + LA + 1);  // in flight while this tile's copies are issued
+      produce(ring_seq_v<LA>(j), vbase, j);
+      if (!alive) break;
+      if (j + LA < ntiles) {
+        produce(ring_seq_k<LA>(j + LA), kbase, j + LA);
+        if (!alive) break;
+      }
+      producers_sync();               // every producer is done reading tile j's ids
+      if (!alive) break;
+      stage_slot(j + LA + 1, next_slot);  // reuses tile j's place
+      producers_sync();
     }
     cp_async_wait<0>();
     if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);
   } else if (warp >= 8) {
     // =========================================================== MMA issuer (warp 8)
-    reg_dec<72>();
+    reg_dec<56>();
     if (warp == 8) {
     const uint32_t idesc_s = idesc_m128<T>(BN, 0);
     const uint32_t idesc_pv = idesc_m128<T>(HD, 1);
@@ -471,8 +475,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       // S_i[t] = Q_i K_t^T : 8 k-steps of 16 elements; both operands K-major
       const uint32_t qa = (q_smem + i * kTcQTileBytes) >> 4;
       const uint32_t kb = (ring + buf * kTcKvTileBytes) >> 4;
-      const uint32_t d_tm = tmem_u + i * 128 + (t & 1) * BN;
-      const uint32_t bar = bar_sf(i, t & 1);
+      const uint32_t d_tm = tmem_u + i * 128 + (t % LA) * BN;
+      const uint32_t bar = bar_sf(i, t % LA);
       if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -489,8 +493,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       // O_i (+)= P V_t : 4 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
       const uint32_t vb = (ring + buf * kTcKvTileBytes) >> 4;
       const uint32_t d_tm = tmem_u + 256 + i * 128;
-      const uint32_t a_tm = tmem_u + i * 128 + (t & 1) * BN;
-      const uint32_t bar = bar_pv(i, t & 1);
+      const uint32_t a_tm = tmem_u + i * 128 + (t % LA) * BN;
+      const uint32_t bar = bar_pv(i, t % LA);
       if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
@@ -515,44 +519,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     };
     if (ntiles > 0) {
       alive = mbar_wait_warp(bar_q, 0, abort_flag);
-      for (int t = 0; t < 2 && t < ntiles && alive; ++t) {
-        acquire(ring_seq_k(t));
+      for (int t = 0; t < LA && t < ntiles && alive; ++t) {
+        acquire(ring_seq_k<LA>(t));
         if (!alive) break;
         for (int i = 0; i < nsub; ++i)
-          if (t < ntiles_sub[i]) issue_s(i, t, ring_seq_k(t) % kTcBufs);
-        release(ring_seq_k(t));
+          if (t < ntiles_sub[i]) issue_s(i, t, ring_seq_k<LA>(t) % kTcBufs);
+        release(ring_seq_k<LA>(t));
       }
     }
 #pragma unroll 1
     for (int j = 0; j < ntiles && alive; ++j) {
-      acquire(ring_seq_v(j));
+      acquire(ring_seq_v<LA>(j));
       if (!alive) break;
       bool k_ready = false;
       for (int i = 0; i < nsub && alive; ++i) {
         if (j < ntiles_sub[i]) {
-          alive = mbar_wait_warp(bar_pf(i, j & 1), (j >> 1) & 1, abort_flag);
+          alive = mbar_wait_warp(bar_pf(i, j % LA), (j / LA) & 1, abort_flag);
           if (!alive) break;
           tc_fence_after();
-          issue_pv(i, j, ring_seq_v(j) % kTcBufs);
+          issue_pv(i, j, ring_seq_v<LA>(j) % kTcBufs);
         }
-        if (j + 2 < ntiles_sub[i]) {
+        if (j + LA < ntiles_sub[i]) {
           if (!k_ready) {
-            acquire(ring_seq_k(j + 2));
+            acquire(ring_seq_k<LA>(j + LA));
             if (!alive) break;
             k_ready = true;
           }
-          issue_s(i, j + 2, ring_seq_k(j + 2) % kTcBufs);
+          issue_s(i, j + LA, ring_seq_k<LA>(j + LA) % kTcBufs);
         }
       }
       if (!alive) break;
-      release(ring_seq_v(j));
-      if (j + 2 < ntiles) release(ring_seq_k(j + 2));
+      release(ring_seq_v<LA>(j));
+      if (j + LA < ntiles) release(ring_seq_k<LA>(j + LA));
     }
     if (!alive && p.status && lane == 0) atomicExch(p.status, 1);
     }
   } else {
     // =========================================================== softmax groups
-    reg_inc<184>();
+    reg_inc<200>();
     const int i = warp >> 2;                 // sub-tile
     const int r = tid & 127;                 // row inside the sub-tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -573,8 +577,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
 
 #pragma unroll 1
     for (int j = 0; j < my_tiles; ++j) {
-      const int sb = j & 1;
-      alive = mbar_wait_warp(bar_sf(i, sb), (j >> 1) & 1, abort_flag);
+      const int sb = j % LA;
+      alive = mbar_wait_warp(bar_sf(i, sb), (j / LA) & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
       const int k0 = kv_lo + j * BN;
@@ -583,6 +587,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       uint32_t v[BN];
       tmem_ld32_at<0>(s_tm + sb * BN, v);
       tmem_ld32_at<32>(s_tm + sb * BN + 32, v);
+      if (BN == 128) {
+        tmem_ld32_at<BN - 64>(s_tm + sb * BN + 64, v);
+        tmem_ld32_at<BN - 32>(s_tm + sb * BN + 96, v);
+      }
       tmem_wait_ld();
       reg_fence(v);
       if (sc_neg) {  // a non-positive scale: fold it into the scores so that max() commutes
@@ -615,7 +623,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
         m_ref = mt;
       }
       if (j > 0 && __any_sync(0xffffffffu, resc)) {
-        alive = mbar_wait_warp(bar_pv(i, (j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
+        alive = mbar_wait_warp(bar_pv(i, (j - 1) % LA), ((j - 1) / LA) & 1, abort_flag);
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
@@ -645,7 +653,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
           l1 += p1;
           pk16[e >> 1] = MmaOp<T>::pack(p0, p1);
         }
-        tmem_st16(s_tm + sb * BN + c * 16, pk16);
+        tmem_st16(s_tm + sb * BN + c * 16, pk16);  // P columns [16c, 16c+16) of this S buffer
       }
       l += l0 + l1;
       tmem_wait_st();
@@ -655,7 +663,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
 
     // ---- epilogue
     if (alive && my_tiles > 0) {
-      alive = mbar_wait_warp(bar_pv(i, (my_tiles - 1) & 1), ((my_tiles - 1) >> 1) & 1, abort_flag);
+      alive = mbar_wait_warp(bar_pv(i, (my_tiles - 1) % LA), ((my_tiles - 1) / LA) & 1, abort_flag);
       if (alive) tc_fence_after();
     }
     if (alive) {

@@ -60,30 +60,35 @@ __device__ __forceinline__ SeqShape load_seq_shape(const PrefillParams& p, int b
   return s;
 }
 
-// Which (sequence, q tile, kv split) a CTA works on.
+// Which (sequence, kv head, q tile, kv split) a CTA works on.
 struct ItemCoord {
-  int b, qt, split;
+  int b, h, qt, split;
   int base;    // id of the sequence's first item; an item's scratch slot is base + qt*nsplit + split
-  bool first;  // exactly one item per sequence has this set (it publishes the plan entry)
+  bool first;  // exactly one CTA per sequence has this set (it publishes the plan entry)
 };
 
 constexpr int kSortedBatchMax = 128;
 
-// Block-wide mapping from a launch rank (0 = scheduled first) to a work item.
+// Block-wide mapping from a launch rank (blockIdx.x; 0 is scheduled first) to a work item.
 // Returns false (for the whole block) if the rank is past the last item.
-// Heavy items get low ranks so that the hardware's in-order CTA dispatch
-// approximates longest-first scheduling: with at most kSortedBatchMax sequences
-// they are ordered by visible key length, longest first, and inside a sequence
-// the last (causally longest) q tile comes first; larger batches keep the
-// natural order, reversed.
+// Order: sequence, then kv head, then q tile / kv split.  CTAs that run at the same
+// time then mostly share one sequence's K/V of one or two heads (L2 reuse), and heavy
+// work gets low ranks so that the hardware's in-order CTA dispatch approximates
+// longest-first scheduling: with at most kSortedBatchMax sequences they are taken by
+// visible key length, longest first, and inside a (sequence, head) the last (causally
+// longest) q tile comes first; larger batches keep the natural order, reversed.
+// `scratch` is block-shared memory the caller does not need yet (4*kSortedBatchMax ints).
 template <int NTHREADS>
-__device__ __forceinline__ bool find_item(const PrefillParams& p, int rank, int BM, ItemCoord& out) {
-  __shared__ int s_res[5];
+__device__ __forceinline__ bool find_item(const PrefillParams& p, int rank, int BM, int* scratch,
+                                          ItemCoord& out) {
+  __shared__ int s_res[6];
   const int tid = threadIdx.x;
   if (tid == 0) s_res[0] = -1;
   if (p.batch <= kSortedBatchMax) {
-    __shared__ int s_key[kSortedBatchMax], s_cnt[kSortedBatchMax], s_nsplit[kSortedBatchMax];
-    __shared__ int s_ord[kSortedBatchMax];
+    int* s_key = scratch;
+    int* s_cnt = scratch + kSortedBatchMax;
+    int* s_nsplit = scratch + 2 * kSortedBatchMax;
+    int* s_ord = scratch + 3 * kSortedBatchMax;
     if (tid < p.batch) {
       const SeqShape s = load_seq_shape(p, tid, BM);
       s_key[tid] = s.hi - s.lo;
@@ -102,18 +107,20 @@ __device__ __forceinline__ bool find_item(const PrefillParams& p, int rank, int 
     }
     __syncthreads();
     if (tid == 0) {
-      int running = 0;
+      int running = 0;  // items (per head) of the sequences before this one
       for (int r = 0; r < p.batch; ++r) {
         const int b = s_ord[r];
         const int c = s_cnt[b];
-        if (rank < running + c) {
-          const int local = rank - running;
+        if (rank < (running + c) * p.hkv) {
+          const int off = rank - running * p.hkv;
+          const int local = off % c;
           const int nsplit = s_nsplit[b];
           s_res[0] = b;
           s_res[1] = c / nsplit - 1 - local / nsplit;  // last q tile first
           s_res[2] = local % nsplit;
           s_res[3] = running;
-          s_res[4] = local == 0;
+          s_res[4] = off == 0;
+          s_res[5] = off / c;
           break;
         }
         running += c;
@@ -121,9 +128,9 @@ __device__ __forceinline__ bool find_item(const PrefillParams& p, int rank, int 
     }
     __syncthreads();
   } else {
-    // natural order, reversed: item = (items launched) - 1 - rank
+    // natural order, reversed: flat id = (CTAs launched) - 1 - rank
     __shared__ int s_warp_tot[NTHREADS / 32];
-    const int item = static_cast<int>(gridDim.x) / p.hkv - 1 - rank;
+    const int flat = static_cast<int>(gridDim.x) - 1 - rank;
     const int lane = tid & 31, warp = tid >> 5;
     __syncthreads();
     int running = 0;
@@ -151,17 +158,19 @@ __device__ __forceinline__ bool find_item(const PrefillParams& p, int rank, int 
         total += t;
       }
       const int excl = running + warp_base + incl - items;
-      if (items > 0 && item >= excl && item < excl + items) {
-        const int local = item - excl;
+      if (items > 0 && flat >= excl * p.hkv && flat < (excl + items) * p.hkv) {
+        const int off = flat - excl * p.hkv;
+        const int local = off % items;
         s_res[0] = b;
         s_res[1] = local / nsplit;
         s_res[2] = local % nsplit;
         s_res[3] = excl;
-        s_res[4] = local == 0;
+        s_res[4] = off == 0;
+        s_res[5] = off / items;
       }
       running += total;
       __syncthreads();
-      if (running > item) break;
+      if (running * p.hkv > flat) break;
     }
     __syncthreads();
   }
@@ -170,6 +179,7 @@ __device__ __forceinline__ bool find_item(const PrefillParams& p, int rank, int 
   out.split = s_res[2];
   out.base = s_res[3];
   out.first = s_res[4] != 0;
+  out.h = s_res[5];
   return out.b >= 0;
 }
 
