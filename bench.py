@@ -45,6 +45,10 @@ import torch  # noqa: E402
 METRIC = "paged decode HBM GB/s + prefill TFLOP/s vs roofline at 1/2/4/8 B200"
 L2_FLUSH_BYTES = 256 << 20
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes per launch of the dominant kernel divided by the workload's algorithmic bytes, from
+# the ncu captures summarised under profiles/ (decode: captured at batch 16 and scaled by the
+# tokens read; prefill: K/V are re-read from L2, not DRAM, across query tiles and heads).
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"decode": 1.004, "prefill": 0.88}
 
 
 def load_peaks():
@@ -119,7 +123,7 @@ BATCH_OVERRIDE = None  # --batch: smaller batch of the same configuration (profi
 
 def make_workload(name: str, device, rank: int):
     from mini_sglang_mlx_b200 import synthetic as S
-    seed_shift = 1000 * rank
+    seed_shift = 0 * rank  # every rank runs the same batch shape and lengths: fixed work per GPU
     kw = {} if BATCH_OVERRIDE is None else {"batch": BATCH_OVERRIDE}
     if name == "cfg1":
         return S.cfg1_decode(seed=101 + seed_shift, device=device, **kw)
@@ -344,10 +348,20 @@ def cpu_work(w, units, flops):
     return sum(2 * w.kv_lens[b] * w.head_dim * 2 + 4 * w.kv_lens[b] + 2 * g * w.head_dim * 2 for b, _ in units)
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every core it may."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_baseline(w, budget_s: float = 12.0):
     wc = cpu_copy_of(w)
     units = cpu_units(wc)
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     cpu_run_units(wc, units[:1])  # warm-up
     t0 = time.perf_counter()
     done, work = 0, 0.0
@@ -382,11 +396,14 @@ def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, pea
     if w.kind == "prefill":
         peak = peaks["bf16_tflops"]
         roof = {"bound": "tensor", "achieved": own, "peak": peak, "unit": "TFLOP/s",
-                "frac": own / peak, "traffic": None, "peak_source": f"{peak_kind} burst bf16"}
+                "frac": own / peak,
+                "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE["prefill"] * w.algorithmic_bytes(),
+                "peak_source": f"{peak_kind} burst bf16"}
     else:
         peak = peaks["hbm_gbs"]
         roof = {"bound": "hbm", "achieved": own, "peak": peak, "unit": "GB/s", "frac": own / peak,
-                "traffic": None, "peak_source": f"{peak_kind} copy bandwidth"}
+                "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE["decode"] * w.algorithmic_bytes(),
+                "peak_source": f"{peak_kind} copy bandwidth"}
     res = {"workload": w.name, "value": value, "unit": unit, "ms_per_step": total_ms / steps,
            "median_ms": statistics.median(per), "min_ms": min(per), "roofline": roof,
            "algorithmic_bytes": w.algorithmic_bytes(), "algorithmic_flops": w.algorithmic_flops(),
@@ -469,7 +486,7 @@ def run_reference(args):
         w = make_workload(args.workload, device, 0)
     wc = cpu_copy_of(w)
     units = cpu_units(wc)
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     # size the per-step sample so that warmup + steps fit in about two minutes
     t0 = time.perf_counter()
     cpu_run_units(wc, units[:1])
