@@ -9,8 +9,8 @@
 //
 //   warps 0-3    softmax group 0: thread r owns row r of sub-tile 0 (TMEM lane r)
 //   warps 4-7    softmax group 1: the same for sub-tile 1
-//   warp  8      MMA issuer (one elected lane issues every tcgen05.mma / commit); 9-11 idle
-//   warps 12-15  producers: gather Q rows and paged K/V token rows with 16-byte
+//   warp  8      MMA issuer (one elected lane issues every tcgen05.mma / commit)
+//   warps 9-15   producers: gather Q rows and paged K/V token rows with 16-byte
 //                cp.async into 128-byte-swizzled shared-memory tiles
 //
 // Per key tile j and sub-tile i:  S_i[j] = Q_i K_j^T  (SS MMA M128 N=BN, fp32 in TMEM)
@@ -41,7 +41,7 @@ constexpr int kTcBM = 256;        // packed query rows per CTA
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
 constexpr int kTcRingBytes = 5 * 128 * 256;  // K/V ring: 5 tiles of 128 tokens or 10 of 64
 constexpr int kTcThreads = 16 * 32;
-constexpr int kTcProducerWarp0 = 12;
+constexpr int kTcProducerWarp0 = 9;   // warps 9..15 copy; more warps keep more bytes in flight
 constexpr int kTcQTileBytes = 128 * 256;                     // one 128-row query sub-tile
 constexpr int kTcSmemBytes = 2 * kTcQTileBytes + kTcRingBytes + 1024;  // + alignment slack
 constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
@@ -277,7 +277,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   static_assert(BN == 64 || BN == 128, "key tile of 64 or 128 tokens");
   constexpr int HD = 128;
   constexpr int BM = kTcBM, SUB = kTcSub;
-  constexpr int NPROD = 128;  // producer threads
+  constexpr int NPROD = (16 - kTcProducerWarp0) * 32;  // producer threads
+  constexpr int PROWS = NPROD / 16;                     // token rows covered by one pass of the producers
   constexpr int LA = BN == 64 ? 2 : 1;        // key tiles S runs ahead of PV (= S buffers per sub-tile)
   constexpr int kTcKvTileBytes = BN * 256;
   constexpr int kTcBufs = kTcRingBytes / kTcKvTileBytes;
@@ -368,12 +369,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   const uint32_t tmem = s_tmem_base;
   volatile int* abort_flag = &s_abort;
 
+  // Register budget: the softmax warps hold a whole score row per thread, the others need
+  // little.  Each warpgroup executes one and the same setmaxnreg instruction.
+  if (warp >= 8) {
+  reg_dec<56>();
   if (warp >= kTcProducerWarp0) {
     // =========================================================== producers
-    reg_dec<56>();
-    const int ptid = tid - kTcProducerWarp0 * 32;  // 0..127
+    const int ptid = tid - kTcProducerWarp0 * 32;  // 0..NPROD-1
     const int chunk = ptid & 15;           // 16-byte chunk of a 256-byte row
-    const int rsub = ptid >> 4;            // 0..7: row inside a group of 8
+    const int rsub = ptid >> 4;            // row inside a pass of PROWS rows
     const T* __restrict__ q = static_cast<const T*>(p.q);
     const unsigned char* __restrict__ kbase = static_cast<const unsigned char*>(p.k_cache);
     const unsigned char* __restrict__ vbase = static_cast<const unsigned char*>(p.v_cache);
@@ -381,8 +385,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     const int64_t head_off = static_cast<int64_t>(h) * (HD * 2);
 
     // Q: rows_valid packed rows, the rest zero
-    for (int i = 0; i < BM / 8; ++i) {
-      const int row = i * 8 + rsub;      // 0..255
+    for (int i = 0; i < (BM + PROWS - 1) / PROWS; ++i) {
+      const int row = i * PROWS + rsub;  // 0..255
       if (row >= nsub * SUB) break;
       const int pk = pk0 + row;
       const int tl = pk / G, g = pk - tl * G;
@@ -395,7 +399,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     }
     cp_async_mbar_arrive(bar_q);
 
-    constexpr int RPT = BN / 8;  // rows of a tile each producer thread copies
+    constexpr int RPT = (BN + PROWS - 1) / PROWS;  // passes over a tile
     // Slot ids are staged in shared memory: thread r fetches the id of row r of a tile (one
     // coalesced load per tile, two tiles ahead of its use), out-of-range ids are reported
     // once and stored as -1 (row treated as absent).  Tile t lives in s_slots[(t % (LA+1)) * BN ..].
@@ -430,7 +434,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       const int* slots = s_slots + (tile % (LA + 1)) * BN;
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
-        const int row = i * 8 + rsub;
+        const int row = i * PROWS + rsub;
+        if (BN % PROWS != 0 && row >= BN) break;
         const int slot = slots[row];
         const bool ok = slot >= 0;
         const int64_t off =
@@ -459,10 +464,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     }
     cp_async_wait<0>();
     if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);
-  } else if (warp >= 8) {
-    // =========================================================== MMA issuer (warp 8)
-    reg_dec<56>();
-    if (warp == 8) {
+  } else if (warp == 8) {
+    // =========================================================== MMA issuer
+    {
     const uint32_t idesc_s = idesc_m128<T>(BN, 0);
     const uint32_t idesc_pv = idesc_m128<T>(HD, 1);
     bool alive = true;
@@ -554,6 +558,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     }
     if (!alive && p.status && lane == 0) atomicExch(p.status, 1);
     }
+  }
   } else {
     // =========================================================== softmax groups
     reg_inc<200>();
