@@ -87,13 +87,22 @@ struct PrefillPlan {
   size_t part_o_bytes, part_ml_bytes, plan_bytes;
 };
 
+// Query blocks that fill at most one 128-row sub-tile (verify, draft blocks) run the
+// one-sub-tile shape (64-token key tiles, two CTAs per SM); longer chunks the two-sub-tile
+// shape with 128-token key tiles.
+bool prefill_short_q(int max_len_extend, int group) {
+  return static_cast<int64_t>(max_len_extend) * group <= msgl::kTcSub;
+}
+
 PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int hkv, int head_dim,
                          int max_len_extend, int window, int sms) {
-  // One CTA of the tensor-core kernel per SM: the key range is split only when the query
-  // tiles alone cannot give every SM a CTA; then about two CTAs per SM are made.
+  // The key range is split only when the query tiles alone cannot give every CTA slot of the
+  // GPU a CTA; then about two CTAs per slot are made.
   PrefillPlan pl{};
   const int G = hq / hkv;
-  const int BM = msgl::kTcBM;
+  const bool short_q = prefill_short_q(max_len_extend, G);
+  const int BM = short_q ? msgl::TcShape<1>::kBM : msgl::TcShape<2>::kBM;
+  const int slots = sms * (short_q ? msgl::TcShape<1>::kCtasPerSm : msgl::TcShape<2>::kCtasPerSm);
   int64_t qtiles = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, 0);
   {  // the other upper bound on the number of query tiles: every sequence at the longest length
     const int64_t per_seq = (static_cast<int64_t>(max_len_extend) * G + BM - 1) / BM;
@@ -105,18 +114,18 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
     if (w < visible) visible = w;
   }
   pl.kv_chunk = 0;
-  if (qtiles * hkv < sms && visible > 0) {
+  if (qtiles * hkv < slots && visible > 0) {
     const int64_t nqt_max = (static_cast<int64_t>(max_len_extend) * G + BM - 1) / BM;
-    int64_t chunk = visible * nqt_max * hkv / (2LL * sms);
+    int64_t chunk = visible * nqt_max * hkv / (2LL * slots);
     if (chunk < 256) chunk = 256;
     chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
   }
   pl.items = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, pl.kv_chunk);
   if (pl.kv_chunk > 0) {
-    const size_t slots = static_cast<size_t>(pl.items) * hkv;
-    pl.part_o_bytes = slots * BM * head_dim * sizeof(float);
-    pl.part_ml_bytes = slots * BM * 2 * sizeof(float);
+    const size_t slots_n = static_cast<size_t>(pl.items) * hkv;
+    pl.part_o_bytes = slots_n * BM * head_dim * sizeof(float);
+    pl.part_ml_bytes = slots_n * BM * 2 * sizeof(float);
     pl.plan_bytes = (static_cast<size_t>(batch) * 2 * sizeof(int) + 255) / 256 * 256;
   }
   return pl;
@@ -361,26 +370,29 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
 
   dim3 grid(static_cast<unsigned>(pl.items * num_kv_heads));
   dim3 mgrid(total_q, num_q_heads);
-  // Query blocks that fill at most one 128-row sub-tile (verify, draft blocks) take the
-  // 64-token key tiles whose score tiles are double-buffered; longer chunks take 128-token
-  // tiles, which read Q from shared memory half as often.
-  const bool short_q = static_cast<int64_t>(max_len_extend) * p.group <= msgl::kTcSub;
+  const bool short_q = prefill_short_q(max_len_extend, p.group);
   cudaError_t e;
-  auto launch = [&](auto kernel, auto merge) -> cudaError_t {
-    cudaError_t err = allow_smem(kernel, msgl::kTcSmemBytes);
+  auto launch = [&](auto kernel, auto merge, int threads, int smem) -> cudaError_t {
+    cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, msgl::kTcThreads, msgl::kTcSmemBytes, s>>>(p);
+    kernel<<<grid, threads, smem, s>>>(p);
     if (pl.kv_chunk > 0) merge<<<mgrid, 128, 0, s>>>(p);
     return cudaSuccess;
   };
+  using S1 = msgl::TcShape<1>;
+  using S2 = msgl::TcShape<2>;
   if (dtype == MSGL_DTYPE_BF16) {
     using T = __nv_bfloat16;
-    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>)
-                : launch(msgl::prefill_tc_kernel<T, 128>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>);
+    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64, 1>, msgl::prefill_merge_kernel<T, 128, S1::kBM>,
+                         S1::kThreads, S1::kSmemBytes)
+                : launch(msgl::prefill_tc_kernel<T, 128, 2>, msgl::prefill_merge_kernel<T, 128, S2::kBM>,
+                         S2::kThreads, S2::kSmemBytes);
   } else {
     using T = __half;
-    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>)
-                : launch(msgl::prefill_tc_kernel<T, 128>, msgl::prefill_merge_kernel<T, 128, msgl::kTcBM>);
+    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64, 1>, msgl::prefill_merge_kernel<T, 128, S1::kBM>,
+                         S1::kThreads, S1::kSmemBytes)
+                : launch(msgl::prefill_tc_kernel<T, 128, 2>, msgl::prefill_merge_kernel<T, 128, S2::kBM>,
+                         S2::kThreads, S2::kSmemBytes);
   }
   if (e != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
