@@ -12,6 +12,11 @@
 //   warp  8      MMA issuer (one elected lane issues every tcgen05.mma / commit)
 //   warps 9-15   producers: gather Q rows and paged K/V token rows with 16-byte
 //                cp.async into 128-byte-swizzled shared-memory tiles
+// The softmax warps raise their register budget (setmaxnreg) so that a thread can
+// hold a whole 128-column score row; the other warps lower theirs.
+// A one-sub-tile shape (128 rows: softmax warps 0-3, MMA warp 4, producers 5-7,
+// half the TMEM and under half the shared memory, two CTAs per SM) serves query
+// blocks that fill at most one sub-tile.
 //
 // Per key tile j and sub-tile i:  S_i[j] = Q_i K_j^T  (SS MMA M128 N=BN, fp32 in TMEM)
 //   -> softmax group i reads its BN-column row (tcgen05.ld), masks boundary
@@ -22,7 +27,7 @@
 // S_i[j+LA] is issued right after PV_i[j] (LA = 1 for BN 128, 2 for BN 64 where
 // S has two buffers per sub-tile).  All hand-offs are mbarriers; every wait is
 // bounded and reports through the status word instead of hanging.
-// TMEM columns: S_i[b] at 128 i + BN b (b = j mod 2 if double-buffered), O_i at 256 + 128 i.
+// TMEM columns: S_i[b] at 128 i + BN b (b = j mod 2 if double-buffered), O_i after the S tiles.
 //
 // Shared-memory tile layout (Q sub-tile, K tile and V tile alike): two halves,
 // half h holding elements [64h, 64h+64) of every row; inside a half row r sits
@@ -37,13 +42,25 @@
 
 namespace msgl {
 
-constexpr int kTcBM = 256;        // packed query rows per CTA
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
-constexpr int kTcRingBytes = 5 * 128 * 256;  // K/V ring: 5 tiles of 128 tokens or 10 of 64
-constexpr int kTcThreads = 16 * 32;
-constexpr int kTcProducerWarp0 = 9;   // warps 9..15 copy; more warps keep more bytes in flight
 constexpr int kTcQTileBytes = 128 * 256;                     // one 128-row query sub-tile
-constexpr int kTcSmemBytes = 2 * kTcQTileBytes + kTcRingBytes + 1024;  // + alignment slack
+
+// Shape of a CTA.  NSUB = 2: 256 query rows, 16 warps, all 512 TMEM columns, 160 KB K/V
+// ring, one CTA per SM.  NSUB = 1: 128 rows, 8 warps, 256 TMEM columns, 64 KB ring, two
+// CTAs per SM (short query blocks are bandwidth-bound: two independent pipelines per SM
+// keep more copies in flight).
+template <int NSUB>
+struct TcShape {
+  static constexpr int kBM = NSUB * kTcSub;                       // packed query rows per CTA
+  static constexpr int kWarps = NSUB == 2 ? 16 : 8;
+  static constexpr int kThreads = kWarps * 32;
+  static constexpr int kMmaWarp = 4 * NSUB;                       // after the softmax warps
+  static constexpr int kProducerWarp0 = kMmaWarp + 1;             // ... the rest copy
+  static constexpr int kRingBytes = NSUB == 2 ? 5 * 128 * 256 : 4 * 64 * 256;
+  static constexpr int kSmemBytes = NSUB * kTcQTileBytes + kRingBytes + 1024;  // + alignment slack
+  static constexpr int kTmemCols = NSUB * 256;
+  static constexpr int kCtasPerSm = NSUB == 2 ? 1 : 2;
+};
 constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -272,16 +289,23 @@ struct TcBarriers {
   uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];
 };
 
-template <typename T, int BN>
-__global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const PrefillParams p) {
+template <typename T, int BN, int NSUB>
+__global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasPerSm)
+    prefill_tc_kernel(const PrefillParams p) {
   static_assert(BN == 64 || BN == 128, "key tile of 64 or 128 tokens");
+  static_assert(NSUB == 2 || BN == 64, "the one-sub-tile shape has TMEM for 64-column score tiles only");
+  using Shape = TcShape<NSUB>;
   constexpr int HD = 128;
-  constexpr int BM = kTcBM, SUB = kTcSub;
-  constexpr int NPROD = (16 - kTcProducerWarp0) * 32;  // producer threads
+  constexpr int BM = Shape::kBM, SUB = kTcSub;
+  constexpr int kTcThreads = Shape::kThreads;
+  constexpr int kMmaWarp = Shape::kMmaWarp;
+  constexpr int kTcProducerWarp0 = Shape::kProducerWarp0;
+  constexpr int NPROD = (Shape::kWarps - kTcProducerWarp0) * 32;  // producer threads
   constexpr int PROWS = NPROD / 16;                     // token rows covered by one pass of the producers
   constexpr int LA = BN == 64 ? 2 : 1;        // key tiles S runs ahead of PV (= S buffers per sub-tile)
   constexpr int kTcKvTileBytes = BN * 256;
-  constexpr int kTcBufs = kTcRingBytes / kTcKvTileBytes;
+  constexpr int kTcBufs = Shape::kRingBytes / kTcKvTileBytes;
+  constexpr uint32_t kOCol = NSUB * 128;      // first TMEM column of the O accumulators
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ TcBarriers bars;
@@ -308,16 +332,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   // ---- geometry of the CTA's rows and of each sub-tile
   const int pk0 = qt * BM;
   const int rows_valid = min(BM, sq.tq * G - pk0);              // >= 1
-  const int nsub = rows_valid > SUB ? 2 : 1;
+  const int nsub = (NSUB == 2 && rows_valid > SUB) ? 2 : 1;
   const int tok_first = pk0 / G;
   const int s_lo = p.kv_chunk > 0 ? sq.lo + split * p.kv_chunk : 0;
   const int s_hi = p.kv_chunk > 0 ? sq.lo + (split + 1) * p.kv_chunk : 0x7fffffff;  // exclusive
   int kv_lo = p.window > 0 ? max(0, sq.prefix + tok_first - p.window + 1) : 0;
   kv_lo = max(kv_lo, s_lo);
   kv_lo = (kv_lo / BN) * BN;
-  int ntiles_sub[2];
+  int ntiles_sub[2] = {0, 0};
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < NSUB; ++i) {
     const int last_row = min(rows_valid, (i + 1) * SUB) - 1;     // last valid row of the sub-tile
     const int tok_last = (pk0 + last_row) / G;
     int hi = p.is_cross ? sq.L : min(sq.L, sq.prefix + tok_last + 1);
@@ -332,7 +356,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   // ---- shared-memory carve-up (1024-byte aligned tiles)
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem0;                                   // 2 sub-tiles
-  const uint32_t ring = smem0 + 2 * kTcQTileBytes;                 // kTcBufs K/V tiles
+  const uint32_t ring = smem0 + NSUB * kTcQTileBytes;              // kTcBufs K/V tiles
 
   const uint32_t bar_q = smem_u32(&bars.q_full);
   auto bar_full = [&](int bf) { return smem_u32(&bars.full[bf]); };
@@ -349,7 +373,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
       mbar_init(bar_full(bf), NPROD);
       mbar_init(bar_empty(bf), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NSUB; ++i) {
       mbar_init(bar_sf(i, 0), 1);
       mbar_init(bar_sf(i, 1), 1);
       mbar_init(bar_pf(i, 0), SUB);
@@ -359,8 +383,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     }
     fence_mbar_init();
   }
-  if (warp == 8) {
-    tmem_alloc(smem_u32(&s_tmem_base), 512);
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&s_tmem_base), Shape::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -371,8 +395,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
 
   // Register budget: the softmax warps hold a whole score row per thread, the others need
   // little.  Each warpgroup executes one and the same setmaxnreg instruction.
-  if (warp >= 8) {
-  reg_dec<56>();
+  if (warp >= kMmaWarp) {
+  if (NSUB == 2) reg_dec<56>();
   if (warp >= kTcProducerWarp0) {
     // =========================================================== producers
     const int ptid = tid - kTcProducerWarp0 * 32;  // 0..NPROD-1
@@ -464,7 +488,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     }
     cp_async_wait<0>();
     if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);
-  } else if (warp == 8) {
+  } else if (warp == kMmaWarp) {
     // =========================================================== MMA issuer
     {
     const uint32_t idesc_s = idesc_m128<T>(BN, 0);
@@ -496,7 +520,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
     auto issue_pv = [&](int i, int t, int buf) {
       // O_i (+)= P V_t : 4 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
       const uint32_t vb = (ring + buf * kTcKvTileBytes) >> 4;
-      const uint32_t d_tm = tmem_u + 256 + i * 128;
+      const uint32_t d_tm = tmem_u + kOCol + i * 128;
       const uint32_t a_tm = tmem_u + i * 128 + (t % LA) * BN;
       const uint32_t bar = bar_pv(i, t % LA);
       if (elect_one()) {
@@ -561,12 +585,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   }
   } else {
     // =========================================================== softmax groups
-    reg_inc<200>();
+    if (NSUB == 2) reg_inc<200>();
     const int i = warp >> 2;                 // sub-tile
     const int r = tid & 127;                 // row inside the sub-tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_tm = tmem + lane_base + i * 128;
-    const uint32_t o_tm = tmem + lane_base + 256 + i * 128;
+    const uint32_t o_tm = tmem + lane_base + kOCol + i * 128;
     const int row = i * SUB + r;
     const int pk = pk0 + row;
     const int tl = pk / G, g = pk - tl * G;
@@ -732,9 +756,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(const Prefill
   // ---- teardown: every role is past its last TMEM access
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, Shape::kTmemCols);
   }
 }
 
