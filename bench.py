@@ -393,17 +393,25 @@ def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, pea
         work_all = float(t.item())
     value = work_all * steps / (total_ms * 1e-3) / div
     own = work * steps / (sum(per) * 1e-3) / div
-    if w.kind == "prefill":
+    # which roofline binds: arithmetic intensity against the ridge of the measured peaks
+    step_s = sum(per) * 1e-3 / steps
+    intensity = w.algorithmic_flops() / max(1, w.algorithmic_bytes())
+    ridge = peaks["bf16_tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+    if w.kind == "prefill" and intensity >= ridge:
         peak = peaks["bf16_tflops"]
-        roof = {"bound": "tensor", "achieved": own, "peak": peak, "unit": "TFLOP/s",
-                "frac": own / peak,
+        ach = w.algorithmic_flops() / step_s / 1e12
+        roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                "frac": ach / peak,
                 "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE["prefill"] * w.algorithmic_bytes(),
                 "peak_source": f"{peak_kind} burst bf16"}
     else:
         peak = peaks["hbm_gbs"]
-        roof = {"bound": "hbm", "achieved": own, "peak": peak, "unit": "GB/s", "frac": own / peak,
-                "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE["decode"] * w.algorithmic_bytes(),
-                "peak_source": f"{peak_kind} copy bandwidth"}
+        ach = w.algorithmic_bytes() / step_s / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                "traffic": (TRAFFIC_PER_ALGORITHMIC_BYTE["decode"] * w.algorithmic_bytes()
+                            if w.kind == "decode" else None),
+                "peak_source": f"{peak_kind} copy bandwidth",
+                "flop_per_byte": intensity, "ridge_flop_per_byte": ridge}
     res = {"workload": w.name, "value": value, "unit": unit, "ms_per_step": total_ms / steps,
            "median_ms": statistics.median(per), "min_ms": min(per), "roofline": roof,
            "algorithmic_bytes": w.algorithmic_bytes(), "algorithmic_flops": w.algorithmic_flops(),
