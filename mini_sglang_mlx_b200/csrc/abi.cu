@@ -181,8 +181,14 @@ int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s) {
     k1<<<grid1, kDecWarps * 32, smem, s>>>(p);
     msgl::decode_merge_kernel<T, 128, kDecCtaTokens><<<grid2, 128, 0, s>>>(p);
   } else {
-    return fail(MSGL_UNSUPPORTED_HEAD_DIM,
-                "paged_decode_attention: head_dim 256 is not built in this library");
+    // head_dim 256: 512-byte token rows, two ring stages per warp (128 KB per CTA)
+    constexpr int kStages256 = 2;
+    auto k1 = msgl::decode_partial_kernel<T, 256, kDecWarps, kStages256>;
+    constexpr int smem = kDecWarps * kStages256 * 2 * msgl::kDecodeGroupTokens * 512;
+    cudaError_t e = allow_smem(k1, smem);
+    if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
+    k1<<<grid1, kDecWarps * 32, smem, s>>>(p);
+    msgl::decode_merge_kernel<T, 256, kDecCtaTokens><<<grid2, 256, 0, s>>>(p);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);

@@ -58,6 +58,21 @@ def test_ragged_batch(hkv, hq, kv_lens):
     assert_close_to_oracle(out, ref, f"decode {kv_lens}")
 
 
+REF_HEAD_CONFIGS_D256 = [(2, 16), (4, 16), (4, 24), (2, 32)]  # the reference's own sweep (head_dim 256)
+
+
+@pytest.mark.parametrize("hkv,hq", REF_HEAD_CONFIGS_D256)
+@pytest.mark.parametrize("kv_lens", [[1], [237], [809], [4096], [8192], [1, 237], [237, 809, 3333, 4096]],
+                         ids=lambda v: str(v))
+def test_head_dim_256_reference_sweep(hkv, hq, kv_lens):
+    """Shapes of mini-sglang-mlx-kernel/test_and_bench/paged_decode_attention.py:18-23, 288, 303-309
+    (identity slots there; permuted here)."""
+    args = make_inputs(kv_lens, hkv, hq, seed=sum(kv_lens), d=256)
+    out = run(*args)
+    ref = O.paged_decode_attention_oracle(*args[:5], 1 / math.sqrt(256))
+    assert_close_to_oracle(out, ref, f"decode D=256 {kv_lens} Hkv={hkv} Hq={hq}")
+
+
 def test_identity_mapping_as_the_reference_tests_use():
     args = make_inputs([809, 3333], 4, 16, permute=False)
     ref = O.paged_decode_attention_oracle(*args[:5], 1 / math.sqrt(128))
