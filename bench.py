@@ -48,7 +48,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch of the dominant kernel divided by the workload's algorithmic bytes, from
 # the ncu captures summarised under profiles/ (decode: captured at batch 16 and scaled by the
 # tokens read; prefill: K/V are re-read from L2, not DRAM, across query tiles and heads).
-TRAFFIC_PER_ALGORITHMIC_BYTE = {"decode": 1.004, "prefill": 0.88}
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"decode": 1.004, "prefill": 0.81}
 
 
 def load_peaks():
@@ -126,7 +126,11 @@ def make_workload(name: str, device, rank: int):
     seed_shift = 0 * rank  # every rank runs the same batch shape and lengths: fixed work per GPU
     kw = {} if BATCH_OVERRIDE is None else {"batch": BATCH_OVERRIDE}
     if name == "cfg1":
-        return S.cfg1_decode(seed=101 + seed_shift, device=device, **kw)
+        from mini_sglang_mlx_b200.attention import compute_num_kv_splits
+        w = S.cfg1_decode(seed=101 + seed_shift, device=device, **kw)
+        w.num_kv_splits = torch.tensor(compute_num_kv_splits(w.kv_lens, w.hkv), dtype=torch.int32,
+                                       device=device)
+        return w
     if name == "cfg2":
         return S.cfg2_prefill(seed=202 + seed_shift, device=device, **kw)
     if name == "cfg3":

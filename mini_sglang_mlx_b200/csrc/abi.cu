@@ -80,6 +80,24 @@ cudaError_t allow_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
+// Launches `kernel` so that its CTAs may be scheduled while the previous kernel of the
+// stream drains (programmatic dependent launch); the kernel itself waits for the previous
+// kernel's memory with griddepcontrol.wait before it reads anything that kernel wrote.
+template <typename P, typename K>
+cudaError_t launch_dependent(K kernel, dim3 grid, dim3 block, cudaStream_t s, const P& params) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 // ---- prefill scheduling decision (shared by the workspace query and the launch)
 struct PrefillPlan {
   int kv_chunk;        // 0 = no kv split
@@ -114,10 +132,15 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
     if (w < visible) visible = w;
   }
   pl.kv_chunk = 0;
-  if (qtiles * hkv < slots && visible > 0) {
-    const int64_t nqt_max = (static_cast<int64_t>(max_len_extend) * G + BM - 1) / BM;
-    int64_t chunk = visible * nqt_max * hkv / (2LL * slots);
-    if (chunk < 256) chunk = 256;
+  // Split the key range only when the query tiles fill at most half of the CTA slots: a
+  // nearly full single wave beats more, shorter CTAs plus a merge pass.
+  if (qtiles * hkv * 2 <= slots && visible > 0) {
+    // measured on cfg3/cfg4 and the small-chunk grid points: splits shorter than 2048 keys cost
+    // more in CTA start-up and merge traffic than they gain in balance
+    const int target = short_q ? 2 : 4;  // CTAs per slot aimed at
+    const int min_chunk = 2048;
+    int64_t chunk = (visible / batch) * (qtiles * hkv) / (static_cast<int64_t>(target) * slots);
+    if (chunk < min_chunk) chunk = min_chunk;
     chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
   }
@@ -179,7 +202,7 @@ int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s) {
     cudaError_t e = allow_smem(k1, smem);
     if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
     k1<<<grid1, kDecWarps * 32, smem, s>>>(p);
-    msgl::decode_merge_kernel<T, 128, kDecCtaTokens><<<grid2, 128, 0, s>>>(p);
+    launch_dependent(msgl::decode_merge_kernel<T, 128, kDecCtaTokens>, grid2, dim3(128), s, p);
   } else {
     // head_dim 256: 512-byte token rows, two ring stages per warp (128 KB per CTA)
     constexpr int kStages256 = 2;
@@ -188,7 +211,7 @@ int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s) {
     cudaError_t e = allow_smem(k1, smem);
     if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
     k1<<<grid1, kDecWarps * 32, smem, s>>>(p);
-    msgl::decode_merge_kernel<T, 256, kDecCtaTokens><<<grid2, 256, 0, s>>>(p);
+    launch_dependent(msgl::decode_merge_kernel<T, 256, kDecCtaTokens>, grid2, dim3(256), s, p);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
@@ -382,7 +405,7 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
     cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
     kernel<<<grid, threads, smem, s>>>(p);
-    if (pl.kv_chunk > 0) merge<<<mgrid, 128, 0, s>>>(p);
+    if (pl.kv_chunk > 0) return launch_dependent(merge, mgrid, dim3(128), s, p);
     return cudaSuccess;
   };
   using S1 = msgl::TcShape<1>;

@@ -111,6 +111,12 @@ __device__ __forceinline__ float quad_sum(float v) {
   return v;
 }
 
+// Programmatic dependent launch: block until the kernel this one depends on has finished
+// and its writes are visible (no-op when launched without the attribute).
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 }  // namespace msgl

@@ -312,6 +312,7 @@ __global__ void __launch_bounds__(HD) decode_merge_kernel(const DecodeParams p) 
   const int L = p.kv_indptr[b + 1] - p.kv_indptr[b];
   const int splits = decode_effective_splits(L, p.num_kv_splits, b, p.max_splits, CTA_TOKENS);
   if (splits <= 1) return;  // pass 1 already wrote the final row
+  grid_dependency_wait();   // the partials come from pass 1
   const int64_t hq_idx = static_cast<int64_t>(b) * p.hq + hq;
   const float* lse = p.part_lse + hq_idx * p.max_splits;
   const float* po = p.part_o + hq_idx * p.max_splits * HD;

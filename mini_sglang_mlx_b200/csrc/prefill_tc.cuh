@@ -781,6 +781,7 @@ __global__ void __launch_bounds__(HD) prefill_merge_kernel(const PrefillParams p
   const int h = hq / G, g = hq - h * G;
   const int pk = (tok - q_begin) * G + g;
   const int qt = pk / BM, r = pk - qt * BM;
+  grid_dependency_wait();  // plan entries and partials come from the attention kernel
   const int base = p.plan[2 * b], nsplit = p.plan[2 * b + 1];
   const int d = threadIdx.x;
   float M = -INFINITY;
