@@ -1,7 +1,6 @@
 // C-ABI entry points of the B200 paged-attention library: argument
 // validation (same rules and message prefixes as the reference host wrappers),
 // scratch layout, launch configuration.  Declarations: include/msgl_b200.h.
-#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -97,47 +96,6 @@ cudaError_t launch_dependent(K kernel, dim3 grid, dim3 block, cudaStream_t s, co
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, params);
-}
-
-// ---- tensor maps for the TMA gathers of the prefill kernel
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled through the runtime's driver entry point table (no link-time
-// dependency on libcuda, which exists only where a driver is installed).
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
-// A KV pool (num_slots, hkv, 128) seen as num_slots*hkv rows of 128 elements; box = 64
-// elements x 1 row (tile::gather4 fetches four such rows per instruction), 128-byte swizzle.
-int make_kv_tensor_map(CUtensorMap* map, const void* pool, int64_t num_slots, int hkv, int dtype,
-                       const char* op) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return fail(MSGL_CUDA_ERROR, std::string(op) + ": cuTensorMapEncodeTiled is unavailable");
-  const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(num_slots) * hkv};
-  const cuuint64_t strides[1] = {256};
-  const cuuint32_t box[2] = {64, 1};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, dtype == MSGL_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        2, const_cast<void*>(pool), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return fail(MSGL_CUDA_ERROR, std::string(op) + ": cuTensorMapEncodeTiled failed with code " +
-                                     std::to_string(static_cast<int>(r)));
-  return MSGL_OK;
 }
 
 // ---- prefill scheduling decision (shared by the workspace query and the launch)
@@ -410,11 +368,6 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
     return fail(MSGL_BAD_ARG, std::string(op) + "workspace too small");
   if (pl.items * num_kv_heads > 0x7fffffffLL || num_q_heads > 65535)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "problem too large for one launch");
-  if (num_slots * num_kv_heads >= 0x7fffffffLL)
-    return fail(MSGL_BAD_SHAPE, std::string(op) + "num_slots * num_kv_heads must be below 2^31");
-  if (num_slots == 0) return fail(MSGL_BAD_SHAPE, std::string(op) + "the KV pool has no slots");
-  if (reinterpret_cast<uintptr_t>(k_cache) % 16 != 0 || reinterpret_cast<uintptr_t>(v_cache) % 16 != 0)
-    return fail(MSGL_BAD_ARG, std::string(op) + "k_cache and v_cache must be 16-byte aligned");
 
   msgl::PrefillParams p{};
   p.q = q;
@@ -442,10 +395,6 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
   p.is_cross = is_cross_attention ? 1 : 0;
   p.window = sliding_window_size;
   p.kv_chunk = pl.kv_chunk;
-  int rc = make_kv_tensor_map(&p.k_map, k_cache, num_slots, num_kv_heads, dtype, "paged_prefill_attention");
-  if (rc != MSGL_OK) return rc;
-  rc = make_kv_tensor_map(&p.v_map, v_cache, num_slots, num_kv_heads, dtype, "paged_prefill_attention");
-  if (rc != MSGL_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   dim3 grid(static_cast<unsigned>(pl.items * num_kv_heads));

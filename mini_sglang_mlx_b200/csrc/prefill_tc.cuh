@@ -10,9 +10,8 @@
 //   warps 0-3    softmax group 0: thread r owns row r of sub-tile 0 (TMEM lane r)
 //   warps 4-7    softmax group 1: the same for sub-tile 1
 //   warp  8      MMA issuer (one elected lane issues every tcgen05.mma / commit)
-//   warp  9      K/V producer: TMA tile::gather4 loads (cp.async.bulk.tensor), four paged
-//                token rows per instruction, into 128-byte-swizzled shared-memory tiles
-//   warps 9-15   Q rows with 16-byte cp.async (once per CTA)
+//   warps 9-15   producers: gather Q rows and paged K/V token rows with 16-byte
+//                cp.async into 128-byte-swizzled shared-memory tiles
 // The softmax warps raise their register budget (setmaxnreg) so that a thread can
 // hold a whole 128-column score row; the other warps lower theirs.
 // A one-sub-tile shape (128 rows: softmax warps 0-3, MMA warp 4, producers 5-7,
@@ -99,23 +98,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
                                                volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
-}
-// Arrive and announce `bytes` of asynchronous (TMA) transactions on `bar`.
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-// TMA gather: rows r0..r3 of a 2-D tensor, box columns starting at element c0, land as four
-// consecutive box rows at `dst` (the tensor map's swizzle applies); completion is counted in
-// bytes on `bar`.  Rows outside the tensor read as zeros.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int r0, int r1, int r2, int r3) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(r0), "r"(r1),
-        "r"(r2), "r"(r3)
-      : "memory");
 }
 // Arrive on `bar` once all cp.async copies issued so far by this thread have landed.
 __device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
@@ -298,6 +280,7 @@ __device__ __forceinline__ int ring_seq_v(int j) { return 2 * j + LA; }
 
 struct TcBarriers {
   uint64_t q_full;
+  uint64_t idx_sync;  // producers only: guards the staged slot ids
   uint64_t full[10], empty[10];
   // [sub-tile][S buffer]: a softmax group may finish tile j+1 before the MMA warp has
   // looked at tile j, so both hand-offs are per S buffer (tiles j and j+2 never overlap)
@@ -308,7 +291,7 @@ struct TcBarriers {
 
 template <typename T, int BN, int NSUB>
 __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasPerSm)
-    prefill_tc_kernel(const __grid_constant__ PrefillParams p) {
+    prefill_tc_kernel(const PrefillParams p) {
   static_assert(BN == 64 || BN == 128, "key tile of 64 or 128 tokens");
   static_assert(NSUB == 2 || BN == 64, "the one-sub-tile shape has TMEM for 64-column score tiles only");
   using Shape = TcShape<NSUB>;
@@ -328,7 +311,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
   __shared__ TcBarriers bars;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ __align__(16) int s_slots[(LA + 2) * BN];  // tensor-map rows of the key tiles in flight
+  __shared__ int s_slots[(LA + 1) * BN];  // slot ids of the key tiles being copied / next to copy
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -385,8 +368,9 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
   if (tid == 0) {
     s_abort = 0;
     mbar_init(bar_q, NPROD);
+    mbar_init(smem_u32(&bars.idx_sync), NPROD);
     for (int bf = 0; bf < kTcBufs; ++bf) {
-      mbar_init(bar_full(bf), 1);  // one arrive.expect_tx per tile; the TMA unit counts the bytes
+      mbar_init(bar_full(bf), NPROD);
       mbar_init(bar_empty(bf), 1);
     }
     for (int i = 0; i < NSUB; ++i) {
@@ -439,72 +423,68 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     }
     cp_async_mbar_arrive(bar_q);
 
-    // ---- K/V: the first producer warp drives the TMA unit; the others are done.
+    constexpr int RPT = (BN + PROWS - 1) / PROWS;  // passes over a tile
+    // Slot ids are staged in shared memory: thread r fetches the id of row r of a tile (one
+    // coalesced load per tile, two tiles ahead of its use), out-of-range ids are reported
+    // once and stored as -1 (row treated as absent).  Tile t lives in s_slots[(t % (LA+1)) * BN ..].
+    const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
+    auto fetch_slot = [&](int tile) -> int {
+      const int t = kv_lo + tile * BN + ptid;
+      return (ptid < BN && tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
+    };
+    auto stage_slot = [&](int tile, int slot) {
+      if (ptid < BN) {
+        if (slot < -1 || static_cast<int64_t>(slot) >= p.num_slots) {
+          if (p.status) atomicExch(p.status, 2);
+          slot = -1;
+        }
+        s_slots[(tile % (LA + 1)) * BN + ptid] = slot;
+      }
+    };
     bool alive = true;
-    if (warp == kTcProducerWarp0) {
-      // Slot ids of a tile are fetched with coalesced loads two tiles ahead of their use and
-      // staged in shared memory as tensor-map row coordinates slot*hkv + h; absent tokens and
-      // out-of-range ids (reported once) become a row past the end of the tensor, which the
-      // TMA unit reads as zeros.  Tile t lives in s_slots[(t % (LA+2)) * BN ..].
-      constexpr int IPL = BN / 32;  // ids per lane and tile
-      const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
-      const int oob_row = static_cast<int>(p.num_slots) * p.hkv;
-      auto fetch_ids = [&](int tile, int (&ids)[IPL]) {
+    uint32_t idx_phase = 0;
+    const uint32_t bar_idx = smem_u32(&bars.idx_sync);
+    auto producers_sync = [&]() {  // bounded barrier among the 128 producer threads
+      mbar_arrive(bar_idx);
+      alive = mbar_wait_warp(bar_idx, idx_phase, abort_flag);
+      idx_phase ^= 1;
+    };
+    // copy one tile into the ring buffer of sequence number `seq`
+    auto produce = [&](int seq, const unsigned char* src_base, int tile) {
+      const int bf = seq % kTcBufs;
+      alive = mbar_wait_warp(bar_empty(bf), ((seq / kTcBufs) & 1) ^ 1, abort_flag);
+      if (!alive) return;
+      const uint32_t dst = ring + bf * kTcKvTileBytes;
+      const int* slots = s_slots + (tile % (LA + 1)) * BN;
 #pragma unroll
-        for (int i = 0; i < IPL; ++i) {
-          const int t = kv_lo + tile * BN + i * 32 + lane;
-          ids[i] = (tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
-        }
-      };
-      auto stage_ids = [&](int tile, const int (&ids)[IPL]) {
-        bool bad = false;
-#pragma unroll
-        for (int i = 0; i < IPL; ++i) {
-          const int slot = ids[i];
-          const bool oob = slot < -1 || static_cast<int64_t>(slot) >= p.num_slots;
-          bad |= oob;
-          s_slots[(tile % (LA + 2)) * BN + i * 32 + lane] = (slot < 0 || oob) ? oob_row : slot * p.hkv + h;
-        }
-        if (bad && p.status) atomicExch(p.status, 2);
-      };
-      // one tile into the ring buffer of sequence number `seq`: BN/4 gathers per 64-element half
-      auto produce = [&](int seq, const CUtensorMap* map, int tile) {
-        const int bf = seq % kTcBufs;
-        alive = mbar_wait_warp(bar_empty(bf), ((seq / kTcBufs) & 1) ^ 1, abort_flag);
-        if (!alive) return;
-        const uint32_t dst = ring + bf * kTcKvTileBytes;
-        const uint32_t bar = bar_full(bf);
-        if (lane == 0) mbar_arrive_expect_tx(bar, kTcKvTileBytes);
-        __syncwarp();
-        const int* rows = s_slots + (tile % (LA + 2)) * BN;
-#pragma unroll
-        for (int i = 0; i < (BN / 4) * 2 / 32; ++i) {
-          const int gi = i * 32 + lane;
-          const int grp = gi % (BN / 4), half = gi / (BN / 4);
-          const int4 r = *reinterpret_cast<const int4*>(rows + 4 * grp);
-          tma_gather4(dst + half * (BN * 128) + grp * 512, map, bar, half * 64, r.x, r.y, r.z, r.w);
-        }
-      };
-      int ids[IPL];
-#pragma unroll
-      for (int t = 0; t <= LA; ++t) {
-        fetch_ids(t, ids);
-        stage_ids(t, ids);
+      for (int i = 0; i < RPT; ++i) {
+        const int row = i * PROWS + rsub;
+        if (BN % PROWS != 0 && row >= BN) break;
+        const int slot = slots[row];
+        const bool ok = slot >= 0;
+        const int64_t off =
+            (ok ? static_cast<int64_t>(slot) * slot_stride + head_off : 0) + chunk * 16;
+        cp_async_16(dst + tc_tile_offset<BN>(row, chunk), src_base + off, ok ? 16 : 0);
       }
-      __syncwarp();
-      for (int t = 0; t < LA && t < ntiles && alive; ++t) produce(ring_seq_k<LA>(t), &p.k_map, t);
+      cp_async_mbar_arrive(bar_full(bf));
+    };
+#pragma unroll
+    for (int t = 0; t <= LA; ++t) stage_slot(t, fetch_slot(t));
+    producers_sync();
+    for (int t = 0; t < LA && t < ntiles && alive; ++t) produce(ring_seq_k<LA>(t), kbase, t);
 #pragma unroll 1
-      for (int j = 0; j < ntiles && alive; ++j) {
-        fetch_ids(j + LA + 1, ids);  // in flight while this tile's gathers are issued
-        produce(ring_seq_v<LA>(j), &p.v_map, j);
+    for (int j = 0; j < ntiles && alive; ++j) {
+      const int next_slot = fetch_slot(j + LA + 1);  // in flight while this tile's copies are issued
+      produce(ring_seq_v<LA>(j), vbase, j);
+      if (!alive) break;
+      if (j + LA < ntiles) {
+        produce(ring_seq_k<LA>(j + LA), kbase, j + LA);
         if (!alive) break;
-        if (j + LA < ntiles) {
-          produce(ring_seq_k<LA>(j + LA), &p.k_map, j + LA);
-          if (!alive) break;
-        }
-        stage_ids(j + LA + 1, ids);  // into the place of tile j-1, no longer read
-        __syncwarp();
       }
+      producers_sync();               // every producer is done reading tile j's ids
+      if (!alive) break;
+      stage_slot(j + LA + 1, next_slot);  // reuses tile j's place
+      producers_sync();
     }
     cp_async_wait<0>();
     if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);

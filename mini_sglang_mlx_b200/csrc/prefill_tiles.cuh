@@ -15,8 +15,6 @@
 // (W == 0 or t >= pos - W + 1).
 #pragma once
 
-#include <cuda.h>  // CUtensorMap (type only; the encode function is looked up at run time)
-
 #include "common.cuh"
 
 namespace msgl {
@@ -39,9 +37,6 @@ struct PrefillParams {
   float scale_log2;
   int is_cross, window;
   int kv_chunk;  // tokens per kv split; 0 = never split
-  // K and V pools as 2-D tensors (num_slots * hkv rows of head_dim elements), box 64 x 1,
-  // 128-byte swizzle: the tile::gather4 loads of the attention kernel fetch 4 rows each
-  CUtensorMap k_map, v_map;
 };
 
 struct SeqShape {
