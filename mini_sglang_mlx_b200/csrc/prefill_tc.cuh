@@ -698,8 +698,10 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     if (alive) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       if (p.kv_chunk == 0) {
-        T* orow = static_cast<T*>(p.out) +
-                  (static_cast<int64_t>(sq.q_begin + tl) * p.hq + static_cast<int64_t>(h) * G + g) * HD;
+        // Each warp stages its 32 output rows (256 bytes each) in the Q sub-tile's shared memory,
+        // free once the last S MMA has completed, then writes them out two whole rows per
+        // instruction; chunk c of row r sits at chunk position c ^ (r & 15) (conflict-free).
+        unsigned char* stage = smem_raw + (smem0 - smem_u32(smem_raw)) + i * kTcQTileBytes;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
@@ -711,15 +713,33 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
 #pragma unroll
             for (int e = 0; e < 32; ++e) v[e] = 0u;
           }
-          if (valid) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              uint4 w;
-              w.x = MmaOp<T>::pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
-              w.y = MmaOp<T>::pack(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
-              w.z = MmaOp<T>::pack(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
-              w.w = MmaOp<T>::pack(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
+          for (int e = 0; e < 32; e += 8) {
+            uint4 w;
+            w.x = MmaOp<T>::pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
+            w.y = MmaOp<T>::pack(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+            w.z = MmaOp<T>::pack(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
+            w.w = MmaOp<T>::pack(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
+            const int chunk = c * 4 + (e >> 3);
+            *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = w;
+          }
+        }
+        __syncwarp();
+        {
+          const int wrow0 = (warp & 3) * 32;   // first row of this warp inside the sub-tile
+          const int chunk = lane & 15;
+#pragma unroll 4
+          for (int rr = lane >> 4; rr < 32; rr += 2) {
+            const int rloc = wrow0 + rr;
+            const int prow = i * SUB + rloc;
+            if (prow < rows_valid) {
+              const int pkr = pk0 + prow;
+              const int tlr = pkr / G, gr = pkr - tlr * G;
+              T* dst = static_cast<T*>(p.out) +
+                       (static_cast<int64_t>(sq.q_begin + tlr) * p.hq + static_cast<int64_t>(h) * G + gr) * HD;
+              const uint4 w =
+                  *reinterpret_cast<const uint4*>(stage + rloc * 256 + ((chunk ^ (rloc & 15)) << 4));
+              *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(dst) + chunk * 16) = w;
             }
           }
         }
