@@ -172,6 +172,17 @@ int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
                            const int32_t* table_idx, const int32_t* kv_indptr,
                            int32_t* kv_indices, int batch, int64_t total_kv, void* stream);
 
+/*
+ * Length of the common prefix of two token-id keys in HOST memory (the first
+ * index at which they differ), elem_bytes 4 (int32) or 8 (int64); -1 for any
+ * other element size.  Used by the radix prefix cache when it walks an edge.
+ * Replaces fast_compare_key
+ * (mini-sglang-mlx-kernel/csrc/fast_compare_key.cpp:9-45, binding
+ * csrc/bindings.cpp:33-35).
+ */
+int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64_t len_b,
+                              int elem_bytes);
+
 #ifdef __cplusplus
 }
 #endif

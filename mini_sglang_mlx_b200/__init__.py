@@ -6,6 +6,7 @@ names and keyword arguments over CUDA ``torch.Tensor`` inputs;
 the reference's ``AttnBackend`` and ``MHAKVCache`` that call them.
 """
 from .kernel import (  # noqa: F401
+    fast_compare_key,
     gather_kv_indices,
     paged_decode_attention,
     paged_prefill_attention,
@@ -17,4 +18,5 @@ __all__ = [
     "paged_prefill_attention",
     "store_kv_cache",
     "gather_kv_indices",
+    "fast_compare_key",
 ]

@@ -479,6 +479,31 @@ int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, co
   return MSGL_OK;
 }
 
+int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64_t len_b,
+                              int elem_bytes) {
+  // host memory; first index at which the two keys differ (their common length if none)
+  if (!a || !b || len_a <= 0 || len_b <= 0) return 0;
+  const int64_t n = len_a < len_b ? len_a : len_b;
+  if (elem_bytes == 8) {
+    const int64_t* x = static_cast<const int64_t*>(a);
+    const int64_t* y = static_cast<const int64_t*>(b);
+    int64_t i = 0;
+    while (i < n && x[i] == y[i]) ++i;
+    return i;
+  }
+  if (elem_bytes == 4) {
+    const int32_t* x = static_cast<const int32_t*>(a);
+    const int32_t* y = static_cast<const int32_t*>(b);
+    int64_t i = 0;
+    // eight ids per step while whole blocks agree, then element by element
+    while (i + 8 <= n && std::memcmp(x + i, y + i, 32) == 0) i += 8;
+    while (i < n && x[i] == y[i]) ++i;
+    return i;
+  }
+  g_last_error = "fast_compare_key: Arrays must be int32 or int64.";
+  return -1;
+}
+
 int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
                            const int32_t* table_idx, const int32_t* kv_indptr,
                            int32_t* kv_indices, int batch, int64_t total_kv, void* stream) {

@@ -21,6 +21,7 @@ __all__ = [
     "paged_prefill_attention",
     "store_kv_cache",
     "gather_kv_indices",
+    "fast_compare_key",
     "device_status",
 ]
 
@@ -212,3 +213,20 @@ def gather_kv_indices(page_table, table_idx, kv_indptr, total_kv: int, *, stream
             page_table.data_ptr(), page_table.stride(0), table_idx.contiguous().data_ptr(),
             kv_indptr.contiguous().data_ptr(), out.data_ptr(), batch, int(total_kv), sh))
     return out
+
+
+def fast_compare_key(a, b) -> int:
+    """Length of the common prefix of two 1-D int32/int64 keys held in host memory
+    (numpy arrays or CPU tensors).  Signature and checks of the reference op:
+    mini-sglang-mlx-kernel/csrc/bindings.cpp:33-35, csrc/fast_compare_key.cpp:9-30."""
+    import numpy as np
+    op = "fast_compare_key"
+    a = a.numpy() if isinstance(a, torch.Tensor) else np.asarray(a)
+    b = b.numpy() if isinstance(b, torch.Tensor) else np.asarray(b)
+    _require(a.ndim == 1 and b.ndim == 1, f"{op}: Both arrays must be 1D.")
+    _require(a.flags["C_CONTIGUOUS"] and b.flags["C_CONTIGUOUS"], f"{op}: Both arrays must be contiguous.")
+    _require(a.dtype == b.dtype, f"{op}: Both arrays must have the same dtype.")
+    _require(a.dtype in (np.int32, np.int64), f"{op}: Arrays must be int32 or int64.")
+    n = _lib.lib().msgl_fast_compare_key(a.ctypes.data, b.ctypes.data, a.shape[0], b.shape[0], a.itemsize)
+    _require(n >= 0, _lib.last_error())
+    return int(n)

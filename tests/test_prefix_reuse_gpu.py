@@ -1,0 +1,85 @@
+"""Prefix reuse end to end on the GPU: slot allocator + radix cache + page table
++ K/V scatter + paged prefill.  A request that shares a prompt prefix with a
+finished one computes only its new tokens (prefix_len = matched length) over the
+cached slots, and must get what a full prefill of its whole prompt gives
+(the flow of mini_sglang_mlx/scheduler/prefill.py:51-107 and
+scheduler/scheduler.py:297-330, without a model: K/V/Q rows are per-token
+embeddings, so they depend on the token id only, as cached K/V must)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import paged_attention_oracle as O
+from tests.helpers import assert_close_to_oracle
+
+pytestmark = pytest.mark.gpu
+
+HQ, HKV, D, VOCAB = 8, 2, 128, 512
+
+
+class _Cfg:
+    head_dim, num_kv_heads, num_qo_heads = D, HKV, HQ
+
+
+class _Prompt:
+    def __init__(self, tokens):
+        self.input_ids = np.asarray(tokens, dtype=np.int32)
+        self.input_len = len(tokens)
+
+
+def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result():
+    from mini_sglang_mlx_b200.attention import AttnBackend
+    from mini_sglang_mlx_b200.core import Batch, BatchPhase, Req
+    from mini_sglang_mlx_b200.kvcache import MHAKVCache
+    from mini_sglang_mlx_b200.scheduler import CacheManager, TableManager
+
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(7)
+    emb_q = torch.randn(VOCAB, HQ, D, generator=g).bfloat16()
+    emb_k = torch.randn(VOCAB, HKV, D, generator=g).bfloat16()
+    emb_v = torch.randn(VOCAB, HKV, D, generator=g).bfloat16()
+
+    num_pages, max_reqs, max_len = 1024, 4, 512
+    pool = MHAKVCache(HKV, 1, D, num_pages + 1, torch.bfloat16)
+    page_table = torch.zeros((max_reqs + 1, max_len), dtype=torch.int32, device=dev)
+    tm = TableManager(max_reqs, page_table)
+    cm = CacheManager(dev, num_pages)
+    be = AttnBackend(_Cfg, pool, page_table)
+
+    rng = np.random.default_rng(3)
+    shared = rng.integers(0, VOCAB, size=300).tolist()
+    prompts = [shared[:200] + rng.integers(0, VOCAB, size=17).tolist(),     # nothing cached yet
+               shared[:150] + rng.integers(0, VOCAB, size=60).tolist(),     # splits the first edge at 150
+               shared[:200] + rng.integers(0, VOCAB, size=1).tolist(),      # one new token
+               shared[:150] + rng.integers(0, VOCAB, size=333).tolist()]    # long suffix
+    expect_cached = [0, 150, 200, 150]
+
+    for tokens, want in zip(prompts, expect_cached):
+        handle, cached = cm.match_req(_Prompt(tokens))
+        assert handle.cached_len == want and cached.is_cuda
+        cm.lock(handle)
+        row = tm.allocate()
+        n = len(tokens)
+        page_table[row, :want] = cached
+        fresh = cm.allocate(n - want)
+        page_table[row, want:n] = fresh
+        req = Req(table_idx=row, cached_len=want, device_len=n)
+        batch = Batch(reqs=[req], phase=BatchPhase.PREFILL, out_loc=fresh)
+        be.prepare_metadata(batch)
+        new = torch.tensor(tokens[want:])
+        out = be.forward(emb_q[new].to(dev), emb_k[new].to(dev), emb_v[new].to(dev), 0, batch)
+
+        # what a prefill of the whole prompt gives, on a private contiguous pool
+        t = torch.tensor(tokens)
+        ref = O.paged_prefill_attention_oracle(
+            emb_q[t], emb_k[t], emb_v[t], np.array([0, n], np.int32), np.array([0, n], np.int32),
+            np.arange(n, dtype=np.int32), np.array([0], np.int32), be.sm_scale)
+        assert_close_to_oracle(out, ref[want:], f"prefix reuse, cached {want} of {n}")
+
+        cm.free_and_cache_finished_req(handle, np.asarray(tokens, np.int32), page_table[row, :n])
+        tm.free(row)
+        cm.check_integrity()
+
+    # the pool holds every distinct prefix once
+    distinct = {tuple(p[: i + 1]) for p in prompts for i in range(len(p))}
+    assert cm.manager.size_info.total_size == len(distinct)
