@@ -72,8 +72,9 @@ def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result():
         # what a prefill of the whole prompt gives, on a private contiguous pool
         t = torch.tensor(tokens)
         ref = O.paged_prefill_attention_oracle(
-            emb_q[t], emb_k[t], emb_v[t], np.array([0, n], np.int32), np.array([0, n], np.int32),
-            np.arange(n, dtype=np.int32), np.array([0], np.int32), be.sm_scale)
+            emb_q[t], emb_k[t], emb_v[t], torch.tensor([0, n], dtype=torch.int32),
+            torch.tensor([0, n], dtype=torch.int32), torch.arange(n, dtype=torch.int32),
+            torch.tensor([0], dtype=torch.int32), be.sm_scale)
         assert_close_to_oracle(out, ref[want:], f"prefix reuse, cached {want} of {n}")
 
         cm.free_and_cache_finished_req(handle, np.asarray(tokens, np.int32), page_table[row, :n])
