@@ -207,6 +207,25 @@ __device__ __forceinline__ void reg_fence(uint32_t (&r)[N]) {
 #pragma unroll
   for (int e = 0; e < N; ++e) asm volatile("" : "+r"(r[e])::"memory");
 }
+// Packed two-float arithmetic (one instruction for two lanes of a register pair).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -499,37 +518,38 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
     const uint64_t desc_hi_k = smem_desc_sw128(0, 16, 1024);                 // Q / K: K-major
     const uint64_t desc_hi_v = smem_desc_sw128(0, BN * 128, 1024);           // V: MN-major
-    auto issue_s = [&](int i, int t, int buf) {
-      // S_i[t] = Q_i K_t^T : 8 k-steps of 16 elements; both operands K-major
+    // The MMAs of one step (PV of tile t_pv and/or S of tile t_s, sub-tile i) are issued by
+    // one elected lane in one go, each group followed by its commit.
+    auto issue_step = [&](int i, bool do_pv, int t_pv, int buf_v, bool do_s, int t_s, int buf_k) {
+      const uint32_t vb = (ring + buf_v * kTcKvTileBytes) >> 4;
+      const uint32_t o_tm = tmem_u + kOCol + i * 128;
+      const uint32_t p_tm = tmem_u + i * 128 + (t_pv % LA) * BN;
       const uint32_t qa = (q_smem + i * kTcQTileBytes) >> 4;
-      const uint32_t kb = (ring + buf * kTcKvTileBytes) >> 4;
-      const uint32_t d_tm = tmem_u + i * 128 + (t % LA) * BN;
-      const uint32_t bar = bar_sf(i, t % LA);
+      const uint32_t kb = (ring + buf_k * kTcKvTileBytes) >> 4;
+      const uint32_t s_tm = tmem_u + i * 128 + (t_s % LA) * BN;
+      const uint32_t bar_o = bar_pv(i, t_pv % LA);
+      const uint32_t bar_s = bar_sf(i, t_s % LA);
       if (elect_one()) {
+        if (do_pv) {
+          // O_i (+)= P V_t : k-steps of 16 tokens; A = P from TMEM, B = V MN-major
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t qoff = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;
-          const uint32_t koff = ((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4;
-          tc_mma_ss(d_tm, desc_hi_k | (qa + qoff), desc_hi_k | (kb + koff), idesc_s,
-                    ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < BN / 16; ++ks) {
+            tc_mma_ts(o_tm, p_tm + ks * 8, desc_hi_v | (vb + ks * (2048 >> 4)), idesc_pv,
+                      (t_pv == 0 && ks == 0) ? 0u : 1u);
+          }
+          tc_commit(bar_o);
         }
-        tc_commit(bar);
-      }
-      __syncwarp();
-    };
-    auto issue_pv = [&](int i, int t, int buf) {
-      // O_i (+)= P V_t : 4 k-steps of 16 tokens; A = P from TMEM, B = V MN-major
-      const uint32_t vb = (ring + buf * kTcKvTileBytes) >> 4;
-      const uint32_t d_tm = tmem_u + kOCol + i * 128;
-      const uint32_t a_tm = tmem_u + i * 128 + (t % LA) * BN;
-      const uint32_t bar = bar_pv(i, t % LA);
-      if (elect_one()) {
+        if (do_s) {
+          // S_i[t] = Q_i K_t^T : 8 k-steps of 16 elements; both operands K-major
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          tc_mma_ts(d_tm, a_tm + ks * 8, desc_hi_v | (vb + ks * (2048 >> 4)), idesc_pv,
-                    (t == 0 && ks == 0) ? 0u : 1u);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t qoff = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;
+            const uint32_t koff = ((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4;
+            tc_mma_ss(s_tm, desc_hi_k | (qa + qoff), desc_hi_k | (kb + koff), idesc_s,
+                      ks > 0 ? 1u : 0u);
+          }
+          tc_commit(bar_s);
         }
-        tc_commit(bar);
       }
       __syncwarp();
     };
@@ -541,44 +561,45 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
         tc_fence_after();
       }
     };
-    auto release = [&](int seq) {
-      if (elect_one()) tc_commit(bar_empty(seq % kTcBufs));
-      __syncwarp();
-    };
     if (ntiles > 0) {
       alive = mbar_wait_warp(bar_q, 0, abort_flag);
       for (int t = 0; t < LA && t < ntiles && alive; ++t) {
-        acquire(ring_seq_k<LA>(t));
+        const int sk = ring_seq_k<LA>(t);
+        acquire(sk);
         if (!alive) break;
         for (int i = 0; i < nsub; ++i)
-          if (t < ntiles_sub[i]) issue_s(i, t, ring_seq_k<LA>(t) % kTcBufs);
-        release(ring_seq_k<LA>(t));
+          issue_step(i, false, 0, 0, t < ntiles_sub[i], t, sk % kTcBufs);
+        if (elect_one()) tc_commit(bar_empty(sk % kTcBufs));
+        __syncwarp();
       }
     }
 #pragma unroll 1
     for (int j = 0; j < ntiles && alive; ++j) {
-      acquire(ring_seq_v<LA>(j));
+      // Both tiles of this step are acquired before the wait for P: the hand-off
+      // P -> PV -> next S of a sub-tile is the chain that bounds the kernel.
+      const int sv = ring_seq_v<LA>(j), sk = ring_seq_k<LA>(j + LA);
+      const bool have_k = j + LA < ntiles;
+      acquire(sv);
       if (!alive) break;
-      bool k_ready = false;
+      if (have_k) {
+        acquire(sk);
+        if (!alive) break;
+      }
       for (int i = 0; i < nsub && alive; ++i) {
-        if (j < ntiles_sub[i]) {
+        const bool do_pv = j < ntiles_sub[i], do_s = j + LA < ntiles_sub[i];
+        if (do_pv) {
           alive = mbar_wait_warp(bar_pf(i, j % LA), (j / LA) & 1, abort_flag);
           if (!alive) break;
           tc_fence_after();
-          issue_pv(i, j, ring_seq_v<LA>(j) % kTcBufs);
         }
-        if (j + LA < ntiles_sub[i]) {
-          if (!k_ready) {
-            acquire(ring_seq_k<LA>(j + LA));
-            if (!alive) break;
-            k_ready = true;
-          }
-          issue_s(i, j + LA, ring_seq_k<LA>(j + LA) % kTcBufs);
-        }
+        if (do_pv || do_s) issue_step(i, do_pv, j, sv % kTcBufs, do_s, j + LA, sk % kTcBufs);
       }
       if (!alive) break;
-      release(ring_seq_v<LA>(j));
-      if (j + LA < ntiles) release(ring_seq_k<LA>(j + LA));
+      if (elect_one()) {
+        tc_commit(bar_empty(sv % kTcBufs));
+        if (have_k) tc_commit(bar_empty(sk % kTcBufs));
+      }
+      __syncwarp();
     }
     if (!alive && p.status && lane == 0) atomicExch(p.status, 1);
     }
@@ -670,21 +691,31 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
       l *= alpha;
       const float nmu = (m_ref == -INFINITY) ? 0.f : -m_ref;
       // ---- P = exp2(s*scale - m_ref) as packed 16-bit pairs over the S columns
-      float l0 = 0.f, l1 = 0.f;
+      // (scale-and-shift and the row sum run as packed two-float operations: the loop is
+      // bounded by instruction issue next to the special-function unit)
+      const uint64_t sc2 = pack_f32x2(sc, sc), nmu2 = pack_f32x2(nmu, nmu);
+      uint64_t la = pack_f32x2(0.f, 0.f), lb = la;
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t pk16[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e]), sc, nmu));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + e + 1]), sc, nmu));
-          l0 += p0;
-          l1 += p1;
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[c * 32 + e]),
+                                            __uint_as_float(v[c * 32 + e + 1])), sc2, nmu2), x0, x1);
+          const float p0 = fast_exp2(x0);
+          const float p1 = fast_exp2(x1);
+          if (e & 2) lb = add_f32x2(lb, pack_f32x2(p0, p1));
+          else la = add_f32x2(la, pack_f32x2(p0, p1));
           pk16[e >> 1] = MmaOp<T>::pack(p0, p1);
         }
         tmem_st16(s_tm + sb * BN + c * 16, pk16);  // P columns [16c, 16c+16) of this S buffer
       }
-      l += l0 + l1;
+      {
+        float l0, l1;
+        unpack_f32x2(add_f32x2(la, lb), l0, l1);
+        l += l0 + l1;
+      }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_pf(i, sb));
