@@ -14,9 +14,11 @@
 //                cp.async into 128-byte-swizzled shared-memory tiles
 // The softmax warps raise their register budget (setmaxnreg) so that a thread can
 // hold a whole 128-column score row; the other warps lower theirs.
-// A one-sub-tile shape (128 rows: softmax warps 0-3, MMA warp 4, producers 5-7,
+// A one-sub-tile shape (128 rows: softmax warps 0-3, MMA warp 4, producers 5-11,
 // half the TMEM and under half the shared memory, two CTAs per SM) serves query
-// blocks that fill at most one sub-tile.
+// blocks that fill at most one sub-tile.  Those shapes are bound by HBM, and a warp
+// sustains only about one 512-byte cp.async instruction per 150 cycles (measured), so
+// the shape keeps as many producer warps as the two-sub-tile one.
 //
 // Per key tile j and sub-tile i:  S_i[j] = Q_i K_j^T  (SS MMA M128 N=BN, fp32 in TMEM)
 //   -> softmax group i reads its BN-column row (tcgen05.ld), masks boundary
@@ -46,13 +48,13 @@ constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
 constexpr int kTcQTileBytes = 128 * 256;                     // one 128-row query sub-tile
 
 // Shape of a CTA.  NSUB = 2: 256 query rows, 16 warps, all 512 TMEM columns, 160 KB K/V
-// ring, one CTA per SM.  NSUB = 1: 128 rows, 8 warps, 256 TMEM columns, 64 KB ring, two
+// ring, one CTA per SM.  NSUB = 1: 128 rows, 12 warps, 256 TMEM columns, 64 KB ring, two
 // CTAs per SM (short query blocks are bandwidth-bound: two independent pipelines per SM
 // keep more copies in flight).
 template <int NSUB>
 struct TcShape {
   static constexpr int kBM = NSUB * kTcSub;                       // packed query rows per CTA
-  static constexpr int kWarps = NSUB == 2 ? 16 : 8;
+  static constexpr int kWarps = NSUB == 2 ? 16 : 12;
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kMmaWarp = 4 * NSUB;                       // after the softmax warps
   static constexpr int kProducerWarp0 = kMmaWarp + 1;             // ... the rest copy
@@ -395,8 +397,8 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     for (int i = 0; i < NSUB; ++i) {
       mbar_init(bar_sf(i, 0), 1);
       mbar_init(bar_sf(i, 1), 1);
-      mbar_init(bar_pf(i, 0), SUB);
-      mbar_init(bar_pf(i, 1), SUB);
+      mbar_init(bar_pf(i, 0), SUB / 32);
+      mbar_init(bar_pf(i, 1), SUB / 32);
       mbar_init(bar_pv(i, 0), 1);
       mbar_init(bar_pv(i, 1), 1);
     }
@@ -415,7 +417,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
   // Register budget: the softmax warps hold a whole score row per thread, the others need
   // little.  Each warpgroup executes one and the same setmaxnreg instruction.
   if (warp >= kMmaWarp) {
-  if (NSUB == 2) reg_dec<56>();
+  reg_dec<56>();
   if (warp >= kTcProducerWarp0) {
     // =========================================================== producers
     const int ptid = tid - kTcProducerWarp0 * 32;  // 0..NPROD-1
@@ -606,7 +608,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
   }
   } else {
     // =========================================================== softmax groups
-    if (NSUB == 2) reg_inc<200>();
+    if (NSUB == 2) reg_inc<200>(); else reg_inc<128>();
     const int i = warp >> 2;                 // sub-tile
     const int r = tid & 127;                 // row inside the sub-tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -718,7 +720,8 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_pf(i, sb));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pf(i, sb));
     }
 
     // ---- epilogue
