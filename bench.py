@@ -524,6 +524,76 @@ def run_ours(args):
         torch.distributed.destroy_process_group()
 
 
+def run_pre_attention_step(args):
+    """`--workload qk_norm_rope_store`: the fused step in front of the attention op (q/k RMSNorm,
+    RoPE, K/V scatter) over one prefill chunk of a Qwen3-8B-shaped layer; HBM-bound, GB/s."""
+    from mini_sglang_mlx_b200 import qk_norm_rope_store
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    peaks, peak_kind = load_peaks()
+    n, hq, hkv, d = args.batch or 32768, 32, 8, 128
+    g = torch.Generator().manual_seed(707)
+    qkv = torch.randn(n, (hq + 2 * hkv) * d, generator=g).bfloat16()
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    pos = torch.arange(n, dtype=torch.int32)
+    num_slots = 2 * n
+    loc = torch.randperm(num_slots, generator=g)[:n].int()
+    qkv_d = qkv.to(device)
+    q = qkv_d[:, : hq * d].view(n, hq, d)
+    k = qkv_d[:, hq * d:(hq + hkv) * d].view(n, hkv, d)
+    v = qkv_d[:, (hq + hkv) * d:].view(n, hkv, d)
+    kc = torch.zeros(num_slots, hkv, d, dtype=torch.bfloat16, device=device)
+    vc = torch.zeros_like(kc)
+    args_d = (qw.to(device), kw.to(device), pos.to(device), loc.to(device), kc, vc)
+    nbytes = n * (2 * hq + 4 * hkv) * d * 2          # q read+write, k and v read, k and v rows written
+    with ClockSampler(device.index) as clocks:
+        for _ in range(args.warmup):
+            qk_norm_rope_store(q, k, v, *args_d, rope_base=1e6)
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        for i in range(args.steps):           # 0.8 GB per step: larger than L2
+            starts[i].record()
+            qk_norm_rope_store(q, k, v, *args_d, rope_base=1e6)
+            ends[i].record()
+        torch.cuda.synchronize()
+    per = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    ms = sum(per) / len(per)
+    cpu = None
+    if not args.no_cpu:
+        from oracle.qk_norm_rope_oracle import qk_norm_rope_store_oracle
+        cores = use_all_host_threads()
+        m = 2048
+        qc = qkv[:m, : hq * d].view(m, hq, d)
+        kc_ = qkv[:m, hq * d:(hq + hkv) * d].view(m, hkv, d)
+        vc_ = qkv[:m, (hq + hkv) * d:].view(m, hkv, d)
+        pool = torch.zeros(num_slots, hkv, d, dtype=torch.bfloat16)
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < 10.0:
+            qk_norm_rope_store_oracle(qc, kc_, vc_, qw, kw, pos[:m], loc[:m], pool, pool.clone(),
+                                      rope_base=1e6, eps=1e-6, rotary_dim=d)
+            reps += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": reps * m * (2 * hq + 4 * hkv) * d * 2 / dt / 1e9, "unit": "GB/s", "cores": cores,
+               "kind": "port", "sample": f"{m} of {n} tokens per pass, torch-CPU restatement of norm, rope, scatter"}
+    ach = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "fused q/k RMSNorm + RoPE + K/V scatter, HBM GB/s", "value": ach, "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"qk_norm_rope_store, {n} tokens, Hq32/Hkv8, D128, fused qkv rows",
+                   "l2": "inputs larger than L2", "algorithmic_bytes_per_step": nbytes},
+        "clocks": clocks.summary(), "e2e": None, "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": f"{peak_kind} copy bandwidth"},
+        "cpu_baseline": cpu}))
+
+
 def run_reference(args):
     """The CPU path the reference's own tests use as ground truth (gather pages, SDPA), as a
     torch-CPU restatement: MLX is not installable here and the Metal kernels need macOS."""
@@ -585,7 +655,9 @@ def main():
     args.warmup = max(args.warmup, 3)
     global BATCH_OVERRIDE
     BATCH_OVERRIDE = args.batch
-    if args.impl == "reference":
+    if args.workload == "qk_norm_rope_store":
+        run_pre_attention_step(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -183,6 +183,29 @@ int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
 int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64_t len_b,
                               int elem_bytes);
 
+/*
+ * The step in front of the attention op, fused into one pass over q, k and v: per-head
+ * RMSNorm of q and k (weights of head_dim elements, same dtype as the data; a null weight
+ * skips that norm), rotary embedding of both (non-interleaved pairs (i, i + rotary_dim/2),
+ * angle = positions[t] * rope_base^(-2i/rotary_dim)), q written back in place, the k rows
+ * written to k_cache[out_loc[t]] and the v rows copied to v_cache[out_loc[t]].
+ * Replaces, for a caller that adopts it, the array ops of
+ * mini_sglang_mlx/models/qwen3.py:58-68 (q_norm, k_norm, rope, rope) plus the
+ * store_kv_cache call of attention/backend.py:117-121; the reference has no fused
+ * operator of this kind (its extension stops at store_kv_cache).
+ * q (n_tokens, Hq, 128), k and v (n_tokens, Hkv, 128) with the given token strides in
+ * elements (rows of a fused qkv projection are fine); caches (num_slots, Hkv, 128) with
+ * cache_row_stride elements per slot.  head_dim must be 128, rotary_dim 64 or 128.
+ * Tokens whose out_loc is outside [0, num_slots) get their q processed and their k/v dropped.
+ */
+int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q_weight,
+                            const void* k_weight, const int32_t* positions,
+                            const int32_t* out_loc, void* k_cache, void* v_cache, int n_tokens,
+                            int num_q_heads, int num_kv_heads, int head_dim, int rotary_dim,
+                            float rope_base, float eps, int64_t num_slots, int64_t q_token_stride,
+                            int64_t k_token_stride, int64_t v_token_stride,
+                            int64_t cache_row_stride, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

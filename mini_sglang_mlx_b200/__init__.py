@@ -7,6 +7,7 @@ the reference's ``AttnBackend`` and ``MHAKVCache`` that call them.
 """
 from .kernel import (  # noqa: F401
     fast_compare_key,
+    qk_norm_rope_store,
     gather_kv_indices,
     paged_decode_attention,
     paged_prefill_attention,
@@ -19,4 +20,5 @@ __all__ = [
     "store_kv_cache",
     "gather_kv_indices",
     "fast_compare_key",
+    "qk_norm_rope_store",
 ]

@@ -36,6 +36,9 @@ SIGNATURES = {
     "msgl_store_kv_cache": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
     "msgl_gather_kv_indices": (_i, [_vp, _i64, _vp, _vp, _vp, _i, _i64, _vp]),
     "msgl_fast_compare_key": (_i64, [_vp, _vp, _i64, _i64, _i]),
+    "msgl_qk_norm_rope_store": (
+        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i64, _i64,
+             _i64, _i64, _i64, _i, _vp]),
 }
 
 

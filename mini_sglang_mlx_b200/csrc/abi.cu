@@ -3,6 +3,7 @@
 // scratch layout, launch configuration.  Declarations: include/msgl_b200.h.
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -11,6 +12,7 @@
 #include "../../include/msgl_b200.h"
 #include "decode_splitkv.cuh"
 #include "prefill_tc.cuh"
+#include "qk_norm_rope.cuh"
 
 namespace {
 
@@ -476,6 +478,67 @@ int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, co
         vec_per_row, crb, irb, num_slots, nullptr);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("store_kv_cache", e);
+  return MSGL_OK;
+}
+
+int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q_weight,
+                            const void* k_weight, const int32_t* positions,
+                            const int32_t* out_loc, void* k_cache, void* v_cache, int n_tokens,
+                            int num_q_heads, int num_kv_heads, int head_dim, int rotary_dim,
+                            float rope_base, float eps, int64_t num_slots, int64_t q_token_stride,
+                            int64_t k_token_stride, int64_t v_token_stride,
+                            int64_t cache_row_stride, int dtype, void* stream) {
+  const char* op = "qk_norm_rope_store: ";
+  if (n_tokens < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0)
+    return fail(MSGL_BAD_SHAPE, std::string(op) +
+                "q must be (n_tokens, num_q_heads, head_dim), k and v (n_tokens, num_kv_heads, head_dim)");
+  if (head_dim != 128)
+    return fail(MSGL_UNSUPPORTED_HEAD_DIM, std::string(op) + "head_dim must be 128");
+  if (rotary_dim != 64 && rotary_dim != 128)
+    return fail(MSGL_BAD_ARG, std::string(op) + "rotary_dim must be 64 or 128");
+  if (dtype != MSGL_DTYPE_BF16 && dtype != MSGL_DTYPE_F16)
+    return fail(MSGL_BAD_DTYPE, std::string(op) + "q, k, v, the weights and the caches must be bf16 or f16");
+  if (!(rope_base > 1.f) || !(eps >= 0.f))
+    return fail(MSGL_BAD_ARG, std::string(op) + "rope_base must be > 1 and eps >= 0");
+  const int64_t kv_row = static_cast<int64_t>(num_kv_heads) * head_dim;
+  if (q_token_stride < static_cast<int64_t>(num_q_heads) * head_dim || k_token_stride < kv_row ||
+      v_token_stride < kv_row || cache_row_stride < kv_row)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "a token or slot stride is smaller than its row");
+  if (n_tokens == 0) return MSGL_OK;
+  if (!q || !k || !v || !positions || !out_loc || !k_cache || !v_cache)
+    return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  auto aligned8 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 8 == 0; };
+  if (!aligned8(v) || !aligned8(v_cache) || v_token_stride % 4 != 0 || cache_row_stride % 4 != 0)
+    return fail(MSGL_BAD_ARG, std::string(op) + "v and v_cache rows must be 8-byte aligned");
+  msgl::QkNormRopeParams p{};
+  p.q = q;
+  p.k = k;
+  p.v = v;
+  p.q_weight = q_weight;
+  p.k_weight = k_weight;
+  p.positions = positions;
+  p.out_loc = out_loc;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.n = n_tokens;
+  p.hq = num_q_heads;
+  p.hkv = num_kv_heads;
+  p.rotary_dim = rotary_dim;
+  p.q_stride = q_token_stride;
+  p.k_stride = k_token_stride;
+  p.v_stride = v_token_stride;
+  p.cache_stride = cache_row_stride;
+  p.num_slots = num_slots;
+  p.log2_base = log2f(rope_base);
+  p.eps = eps;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = 128;
+  if (dtype == MSGL_DTYPE_BF16)
+    msgl::qk_norm_rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(p);
+  else
+    msgl::qk_norm_rope_store_kernel<__half><<<n_tokens, threads, 0, s>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("qk_norm_rope_store", e);
   return MSGL_OK;
 }
 

@@ -22,6 +22,7 @@ __all__ = [
     "store_kv_cache",
     "gather_kv_indices",
     "fast_compare_key",
+    "qk_norm_rope_store",
     "device_status",
 ]
 
@@ -190,6 +191,55 @@ def store_kv_cache(k_cache, v_cache, indices, k, v, *, stream=None) -> None:
         _lib.check(_lib.lib().msgl_store_kv_cache(
             k_cache.data_ptr(), v_cache.data_ptr(), indices.data_ptr(), k.data_ptr(), v.data_ptr(),
             length, hkv, d, num_slots, k_cache.stride(0), k.stride(0), _DTYPES[k_cache.dtype], sh))
+
+
+def qk_norm_rope_store(q, k, v, q_weight, k_weight, positions, out_loc, k_cache, v_cache, *,
+                       rope_base: float, eps: float = 1e-6, rotary_dim: Optional[int] = None,
+                       stream=None) -> torch.Tensor:
+    """Per-head RMSNorm of q and k, rotary embedding of both, and the K/V scatter, in one pass.
+
+    What a Qwen3 attention layer does between its projections and the attention call
+    (mini_sglang_mlx/models/qwen3.py:58-68: ``q_norm``, ``k_norm``, ``rope(q)``, ``rope(k)``)
+    followed by the store of ``AttnBackend.forward`` (attention/backend.py:117-121).  ``q`` is
+    updated in place and returned; the new K rows go to ``k_cache[out_loc]`` normalised and
+    rotated, the V rows to ``v_cache[out_loc]`` unchanged.  ``q``, ``k``, ``v`` may be views
+    into one fused projection output (dense heads, any token stride).  ``q_weight`` /
+    ``k_weight``: (head_dim,) or None to skip that norm.
+    """
+    op = "qk_norm_rope_store"
+    _require(q.dim() == 3 and k.dim() == 3 and v.dim() == 3,
+             f"{op}: q must be (n_tokens, num_q_heads, head_dim), k and v (n_tokens, num_kv_heads, head_dim)")
+    n, hq, d = q.shape
+    hkv = k.shape[1]
+    _require(tuple(k.shape) == (n, hkv, d) and tuple(v.shape) == (n, hkv, d),
+             f"{op}: k and v shape must be (n_tokens, num_kv_heads, head_dim)")
+    _require(q.dtype in _DTYPES and all(t.dtype == q.dtype for t in (k, v, k_cache, v_cache)),
+             f"{op}: q, k, v and the caches must share a dtype, float16 or bfloat16")
+    for wt in (q_weight, k_weight):
+        _require(wt is None or (wt.dtype == q.dtype and tuple(wt.shape) == (d,) and wt.is_contiguous()),
+                 f"{op}: a norm weight must be (head_dim,) in the data dtype")
+    _require(k_cache.dim() == 3 and tuple(k_cache.shape[1:]) == (hkv, d) and v_cache.shape == k_cache.shape,
+             f"{op}: k_cache and v_cache must be (num_pages, num_kv_heads, head_dim)")
+    _require(positions.dtype == torch.int32 and out_loc.dtype == torch.int32
+             and tuple(positions.shape) == (n,) and tuple(out_loc.shape) == (n,)
+             and positions.is_contiguous() and out_loc.is_contiguous(),
+             f"{op}: positions and out_loc must be contiguous int32 of n_tokens elements")
+    for t in (q, k, v, k_cache, v_cache):
+        _require(t.stride(2) == 1 and t.stride(1) == d, f"{op}: rows must be dense")
+    _require(k_cache.stride(0) == v_cache.stride(0), f"{op}: the two caches must share their row stride")
+    _require(q.is_cuda and all(t.device == q.device for t in (k, v, positions, out_loc, k_cache, v_cache)),
+             f"{op}: tensors must live on the same CUDA device")
+    rd = d if rotary_dim is None else int(rotary_dim)
+    sh = _stream_handle(stream, q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().msgl_qk_norm_rope_store(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            q_weight.data_ptr() if q_weight is not None else None,
+            k_weight.data_ptr() if k_weight is not None else None,
+            positions.data_ptr(), out_loc.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            n, hq, hkv, d, rd, float(rope_base), float(eps), k_cache.shape[0],
+            q.stride(0), k.stride(0), v.stride(0), k_cache.stride(0), _DTYPES[q.dtype], sh))
+    return q
 
 
 def gather_kv_indices(page_table, table_idx, kv_indptr, total_kv: int, *, stream=None):

@@ -117,3 +117,26 @@ def test_empty_and_fully_masked_rows_are_zero():
         q, kc, kc, torch.tensor([0, 1, 2], dtype=torch.int32), torch.tensor([0, 0, 2], dtype=torch.int32),
         torch.tensor([1, 2], dtype=torch.int32), torch.tensor([0, -5], dtype=torch.int32), 1.0)
     assert torch.count_nonzero(out) == 0
+
+
+def test_norm_and_rope_restatements_match_the_transformers_implementations():
+    """The q/k RMSNorm and the non-interleaved RoPE of oracle/qk_norm_rope_oracle.py against the
+    independent implementations of the same two formulas that ship with transformers."""
+    tq = pytest.importorskip("transformers.models.qwen3.modeling_qwen3")
+    from oracle.qk_norm_rope_oracle import rms_norm_oracle, rope_oracle
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(11, 8, 128, generator=g)
+    pos = torch.randint(0, 5000, (11,), generator=g)
+    base = 1e6
+    inv = base ** (-torch.arange(0, 128, 2, dtype=torch.float32) / 128)
+    fr = pos.float()[:, None] * inv[None, :]
+    emb = torch.cat([fr, fr], -1)
+    xh = x.permute(1, 0, 2)[None]                      # (batch 1, heads, tokens, d)
+    out, _ = tq.apply_rotary_pos_emb(xh, xh, emb.cos()[None], emb.sin()[None])
+    assert (out[0].permute(1, 0, 2) - rope_oracle(x, pos, base, 128)).abs().max().item() < 1e-5
+    norm = tq.Qwen3RMSNorm(128, eps=1e-6)
+    norm.weight.data = 1 + 0.1 * torch.randn(128, generator=g)
+    assert (norm(x) - rms_norm_oracle(x, norm.weight.data, 1e-6)).abs().max().item() < 1e-6
+    # partial rotary: the upper elements pass through
+    half = rope_oracle(x, pos, base, 64)
+    assert torch.equal(half[..., 64:], x[..., 64:])
