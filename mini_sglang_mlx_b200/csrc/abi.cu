@@ -508,8 +508,10 @@ int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q
   if (!q || !k || !v || !positions || !out_loc || !k_cache || !v_cache)
     return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
   auto aligned8 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 8 == 0; };
-  if (!aligned8(v) || !aligned8(v_cache) || v_token_stride % 4 != 0 || cache_row_stride % 4 != 0)
-    return fail(MSGL_BAD_ARG, std::string(op) + "v and v_cache rows must be 8-byte aligned");
+  if (!aligned8(q) || !aligned8(k) || !aligned8(v) || !aligned8(k_cache) || !aligned8(v_cache) ||
+      q_token_stride % 4 != 0 || k_token_stride % 4 != 0 || v_token_stride % 4 != 0 ||
+      cache_row_stride % 4 != 0)
+    return fail(MSGL_BAD_ARG, std::string(op) + "q, k, v and cache rows must be 8-byte aligned");
   msgl::QkNormRopeParams p{};
   p.q = q;
   p.k = k;
@@ -532,7 +534,9 @@ int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q
   p.log2_base = log2f(rope_base);
   p.eps = eps;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int threads = 128;
+  const int rows = num_q_heads + 2 * num_kv_heads;
+  int threads = 32 * ((rows + 15) / 16);   // a warp per sixteen rows: two passes of eight
+  if (threads > 256) threads = 256;
   if (dtype == MSGL_DTYPE_BF16)
     msgl::qk_norm_rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(p);
   else

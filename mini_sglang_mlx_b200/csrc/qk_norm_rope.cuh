@@ -12,12 +12,12 @@
 // non-interleaved layout (pairs (i, i + rd/2), angle = position * base^(-2i/rd)) in fp32,
 // rounded once more.  head_dim 128, rotary_dim 64 or 128.
 //
-// One CTA of four warps per token, the warps independent of one another (no shared memory,
-// no CTA barrier): each takes four (token, head) rows at a time with the next four already
-// in flight (the kernel is bound by HBM and needs the bytes in flight), and computes the two
-// rotary angles its lanes need itself.  Lane l holds elements 2l, 2l+1 and 64+2l, 65+2l of a
-// row: 128-byte warp accesses, and for rotary_dim 128 both members of a rotary pair sit in
-// the same lane (for rotary_dim 64 the partner is lane l ^ 16).
+// One CTA per token, its warps independent of one another (no shared memory, no CTA
+// barrier).  A half-warp owns a row: lane hl of it holds elements 4hl..4hl+3 and
+// 64+4hl..64+4hl+3 (8-byte accesses, 128 bytes per half-warp), so for rotary_dim 128 both
+// members of a rotary pair sit in the same lane (for rotary_dim 64 the partner is lane ^ 8).
+// A warp has eight rows in flight and the next eight prefetched (the kernel is bound by HBM
+// and needs the bytes in flight), and computes the four rotary angles its lanes need itself.
 #pragma once
 
 #include "common.cuh"
@@ -65,22 +65,30 @@ template <>
 struct Pair16<__nv_bfloat16> {
   using type = __nv_bfloat162;
   __device__ __forceinline__ static float2 unpack(type v) { return __bfloat1622float2(v); }
+  __device__ __forceinline__ static float2 from_bits(uint32_t v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+  }
   __device__ __forceinline__ static type pack(float a, float b) { return __floats2bfloat162_rn(a, b); }
 };
 template <>
 struct Pair16<__half> {
   using type = __half2;
   __device__ __forceinline__ static float2 unpack(type v) { return __half22float2(v); }
+  __device__ __forceinline__ static float2 from_bits(uint32_t v) {
+    return make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xffffu))),
+                       __half2float(__ushort_as_half(static_cast<unsigned short>(v >> 16))));
+  }
   __device__ __forceinline__ static type pack(float a, float b) { return __floats2half2_rn(a, b); }
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkNormRopeParams p) {
+__global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRopeParams p) {
   constexpr int HD = 128;
-  constexpr int RU = 4;  // rows a warp has in flight
+  constexpr int RU = 4;  // row pairs a warp has in flight (a half-warp per row)
   using P2 = typename Pair16<T>::type;
   const int tok = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int hl = lane & 15, side = lane >> 4;   // position inside the half-warp, which row of the pair
   const int half = p.rotary_dim >> 1;
   const int n_qk = p.hq + p.hkv, rows = n_qk + p.hkv;
   auto row_ptr = [&](int row) -> const T* {
@@ -88,90 +96,113 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkNormRop
     if (row < n_qk) return static_cast<const T*>(p.k) + tok * p.k_stride + (row - p.hq) * HD;
     return static_cast<const T*>(p.v) + tok * p.v_stride + (row - n_qk) * HD;
   };
-  auto load_rows = [&](int row0, P2 (&lo)[RU], P2 (&hi)[RU]) {
+  // lane (side, hl) holds elements 4hl..4hl+3 and 64+4hl..64+4hl+3 of row (first + 2u + side)
+  auto load_rows = [&](int first, uint2 (&lo)[RU], uint2 (&hi)[RU]) {
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
-      if (row0 + u < rows) {
-        const P2* src = reinterpret_cast<const P2*>(row_ptr(row0 + u));
-        lo[u] = src[lane];
-        hi[u] = src[32 + lane];
+      const int row = first + 2 * u + side;
+      if (row < rows) {
+        const uint2* src = reinterpret_cast<const uint2*>(row_ptr(row));
+        lo[u] = src[hl];
+        hi[u] = src[16 + hl];
       }
     }
   };
   // the first rows are on their way while the token's angles are worked out
-  P2 lo[RU], hi[RU];
-  load_rows(warp * RU, lo, hi);
+  uint2 lo[RU], hi[RU];
+  load_rows(warp * 2 * RU, lo, hi);
   const int slot = p.out_loc[tok];
   const bool slot_ok = slot >= 0 && slot < p.num_slots;
-  // this lane's two rotary frequencies: pairs (2l, 2l+1) of the first half for rotary_dim 128,
-  // (2(l & 15), +1) for rotary_dim 64.  angle = position * base^(-2i/rd): the product is taken
-  // in fp32 as the reference does.
-  const int f0 = half == 64 ? 2 * lane : 2 * (lane & 15);
+  // this lane's four rotary frequencies: pair index i = 4hl + e of the first half for
+  // rotary_dim 128, 4(hl & 7) + e for rotary_dim 64.  angle = position * base^(-2i/rd): the
+  // product is taken in fp32 as the reference does.
+  const int f0 = half == 64 ? 4 * hl : 4 * (hl & 7);
   const float posf = static_cast<float>(p.positions[tok]);
   const float inv_rd = 1.f / static_cast<float>(p.rotary_dim);
-  float c0, s0, c1, s1;
-  sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * f0) * inv_rd)), s0, c0);
-  sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * f0 + 2) * inv_rd)), s1, c1);
-  float w_lo[2][2], w_hi[2][2];  // [q or k][element of the pair]
+  float cs[4], sn[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + e)) * inv_rd)), sn[e], cs[e]);
+  float w_lo[2][4], w_hi[2][4];  // [q or k][element]
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const T* w = static_cast<const T*>(t == 0 ? p.q_weight : p.k_weight);
-    if (w) {
-      const float2 a = Pair16<T>::unpack(reinterpret_cast<const P2*>(w)[lane]);
-      const float2 b = Pair16<T>::unpack(reinterpret_cast<const P2*>(w)[32 + lane]);
-      w_lo[t][0] = a.x; w_lo[t][1] = a.y; w_hi[t][0] = b.x; w_hi[t][1] = b.y;
-    } else {
-      w_lo[t][0] = w_lo[t][1] = w_hi[t][0] = w_hi[t][1] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      w_lo[t][e] = w ? to_f32(w[4 * hl + e]) : 0.f;
+      w_hi[t][e] = w ? to_f32(w[64 + 4 * hl + e]) : 0.f;
     }
   }
+  auto unpack4 = [](uint2 v, float (&x)[4]) {
+    const float2 a = Pair16<T>::from_bits(v.x), b = Pair16<T>::from_bits(v.y);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  };
+  auto pack4 = [](const float (&x)[4]) -> uint2 {
+    return make_uint2(MmaOp<T>::pack(x[0], x[1]), MmaOp<T>::pack(x[2], x[3]));
+  };
 
-  for (int row0 = warp * RU; row0 < rows; row0 += nwarps * RU) {
-    P2 nlo[RU], nhi[RU];   // the next four rows, in flight while these are processed
-    load_rows(row0 + nwarps * RU, nlo, nhi);
+  for (int first = warp * 2 * RU; first < rows; first += nwarps * 2 * RU) {
+    uint2 nlo[RU], nhi[RU];   // the next rows, in flight while these are processed
+    load_rows(first + nwarps * 2 * RU, nlo, nhi);
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
-      const int row = row0 + u;
-      if (row >= rows) break;
-      if (row >= n_qk) {
-        // ---- V row: copy into the pool
-        if (slot_ok) {
-          T* dst = static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD;
-          reinterpret_cast<P2*>(dst)[lane] = lo[u];
-          reinterpret_cast<P2*>(dst)[32 + lane] = hi[u];
-        }
-        continue;
-      }
-      const bool is_q = row < p.hq;
-      if (!is_q && !slot_ok) continue;
-      T* dst = is_q ? static_cast<T*>(p.q) + tok * p.q_stride + row * HD
-                    : static_cast<T*>(p.k_cache) + slot * p.cache_stride + (row - p.hq) * HD;
-      const int wi = is_q ? 0 : 1;
-      float2 a = Pair16<T>::unpack(lo[u]), b = Pair16<T>::unpack(hi[u]);
-      if ((is_q ? p.q_weight : p.k_weight) != nullptr) {
-        float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+      // the two half-warps may hold rows of different kinds (the last k row and the first v
+      // row), so every branch below is taken per half-warp and the shuffles stay inside it
+      const int row = first + 2 * u + side;
+      const bool live = row < rows;
+      const bool is_v = live && row >= n_qk;
+      const bool is_q = live && row < p.hq;
+      const bool has_w = live && !is_v && (is_q ? p.q_weight : p.k_weight) != nullptr;
+      float a[4], b[4];
+      unpack4(live ? lo[u] : make_uint2(0u, 0u), a);
+      unpack4(live ? hi[u] : make_uint2(0u, 0u), b);
+      float ss = 0.f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (has_w) {
         const float inv = rsqrtf(ss * (1.f / HD) + p.eps);
+        float na[4], nb[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          na[e] = a[e] * inv * (is_q ? w_lo[0][e] : w_lo[1][e]);
+          nb[e] = b[e] * inv * (is_q ? w_hi[0][e] : w_hi[1][e]);
+        }
         // rounded as the reference's materialised norm output is
-        a = Pair16<T>::unpack(Pair16<T>::pack(a.x * inv * w_lo[wi][0], a.y * inv * w_lo[wi][1]));
-        b = Pair16<T>::unpack(Pair16<T>::pack(b.x * inv * w_hi[wi][0], b.y * inv * w_hi[wi][1]));
+        unpack4(pack4(na), a);
+        unpack4(pack4(nb), b);
       }
-      if (half == 64) {
-        // pairs (2l, 64+2l) and (2l+1, 65+2l), both in this lane
-        const float ax = a.x * c0 - b.x * s0, bx = a.x * s0 + b.x * c0;
-        const float ay = a.y * c1 - b.y * s1, by = a.y * s1 + b.y * c1;
-        a = make_float2(ax, ay);
-        b = make_float2(bx, by);
+      // rotary_dim 64: pairs (i, i+32) inside the first 64 elements; lanes hl < 8 hold the
+      // first members, hl >= 8 the second (partner lane ^ 8); the upper 64 pass through
+      float other[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) other[e] = __shfl_xor_sync(0xffffffffu, a[e], 8);
+      if (!is_v) {
+        if (half == 64) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {  // pairs (4hl+e, 64+4hl+e), both in this lane
+            const float x = a[e], y = b[e];
+            a[e] = x * cs[e] - y * sn[e];
+            b[e] = x * sn[e] + y * cs[e];
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            a[e] = hl < 8 ? a[e] * cs[e] - other[e] * sn[e] : other[e] * sn[e] + a[e] * cs[e];
+        }
+      }
+      if (!live) continue;
+      T* dst;
+      if (is_q) {
+        dst = static_cast<T*>(p.q) + tok * p.q_stride + row * HD;
       } else {
-        // rotary_dim 64: pairs (i, i+32) inside the first 64 elements; lanes 0-15 hold the
-        // first members, lanes 16-31 the second; the upper 64 elements pass through
-        const float ox = __shfl_xor_sync(0xffffffffu, a.x, 16);
-        const float oy = __shfl_xor_sync(0xffffffffu, a.y, 16);
-        if (lane < 16) a = make_float2(a.x * c0 - ox * s0, a.y * c1 - oy * s1);
-        else a = make_float2(ox * s0 + a.x * c0, oy * s1 + a.y * c1);
+        if (!slot_ok) continue;
+        dst = is_v ? static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD
+                   : static_cast<T*>(p.k_cache) + slot * p.cache_stride + (row - p.hq) * HD;
       }
-      reinterpret_cast<P2*>(dst)[lane] = Pair16<T>::pack(a.x, a.y);
-      reinterpret_cast<P2*>(dst)[32 + lane] = Pair16<T>::pack(b.x, b.y);
+      reinterpret_cast<uint2*>(dst)[hl] = is_v ? lo[u] : pack4(a);
+      reinterpret_cast<uint2*>(dst)[16 + hl] = is_v ? hi[u] : pack4(b);
     }
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
