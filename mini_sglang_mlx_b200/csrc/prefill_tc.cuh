@@ -209,25 +209,6 @@ __device__ __forceinline__ void reg_fence(uint32_t (&r)[N]) {
 #pragma unroll
   for (int e = 0; e < N; ++e) asm volatile("" : "+r"(r[e])::"memory");
 }
-// Packed two-float arithmetic (one instruction for two lanes of a register pair).
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -616,7 +597,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     const uint32_t o_tm = tmem + lane_base + kOCol + i * 128;
     const int row = i * SUB + r;
     const int pk = pk0 + row;
-    const int tl = pk / G, g = pk - tl * G;
+    const int tl = pk / G;
     const bool valid = row < rows_valid;
     const int pos = sq.prefix + tl;
     const int vhi = min(p.is_cross ? sq.L - 1 : min(pos, sq.L - 1), s_hi - 1);

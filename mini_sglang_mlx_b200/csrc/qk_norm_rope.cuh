@@ -123,22 +123,30 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
 #pragma unroll
   for (int e = 0; e < 4; ++e)
     sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + e)) * inv_rd)), sn[e], cs[e]);
-  float w_lo[2][4], w_hi[2][4];  // [q or k][element]
+  // norm weights and rotation factors as packed pairs of floats: elements (0,1) and (2,3) of
+  // the lane's low and high quadruple
+  uint64_t wq[4], wk[4];   // [lo01, lo23, hi01, hi23]
+  {
+    const T* w = static_cast<const T*>(p.q_weight);
+    const T* x = static_cast<const T*>(p.k_weight);
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const T* w = static_cast<const T*>(t == 0 ? p.q_weight : p.k_weight);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      w_lo[t][e] = w ? to_f32(w[4 * hl + e]) : 0.f;
-      w_hi[t][e] = w ? to_f32(w[64 + 4 * hl + e]) : 0.f;
+    for (int h2 = 0; h2 < 4; ++h2) {
+      const int e0 = (h2 >> 1) * 64 + 4 * hl + (h2 & 1) * 2;
+      wq[h2] = w ? pack_f32x2(to_f32(w[e0]), to_f32(w[e0 + 1])) : 0ull;
+      wk[h2] = x ? pack_f32x2(to_f32(x[e0]), to_f32(x[e0 + 1])) : 0ull;
     }
   }
-  auto unpack4 = [](uint2 v, float (&x)[4]) {
-    const float2 a = Pair16<T>::from_bits(v.x), b = Pair16<T>::from_bits(v.y);
-    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  const uint64_t cs01 = pack_f32x2(cs[0], cs[1]), cs23 = pack_f32x2(cs[2], cs[3]);
+  const uint64_t sn01 = pack_f32x2(sn[0], sn[1]), sn23 = pack_f32x2(sn[2], sn[3]);
+  const uint64_t ng01 = pack_f32x2(-sn[0], -sn[1]), ng23 = pack_f32x2(-sn[2], -sn[3]);
+  auto from_bits2 = [](uint32_t v) -> uint64_t {
+    const float2 f = Pair16<T>::from_bits(v);
+    return pack_f32x2(f.x, f.y);
   };
-  auto pack4 = [](const float (&x)[4]) -> uint2 {
-    return make_uint2(MmaOp<T>::pack(x[0], x[1]), MmaOp<T>::pack(x[2], x[3]));
+  auto to_bits2 = [](uint64_t v) -> uint32_t {
+    float x, y;
+    unpack_f32x2(v, x, y);
+    return MmaOp<T>::pack(x, y);
   };
 
   for (int first = warp * 2 * RU; first < rows; first += nwarps * 2 * RU) {
@@ -146,51 +154,70 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
     load_rows(first + nwarps * 2 * RU, nlo, nhi);
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
-      // the two half-warps may hold rows of different kinds (the last k row and the first v
-      // row), so every branch below is taken per half-warp and the shuffles stay inside it
       const int row = first + 2 * u + side;
       const bool live = row < rows;
+      if (first + 2 * u >= n_qk) {
+        // ---- both rows of the pair are V rows (or past the end): copy into the pool
+        if (live && slot_ok) {
+          T* dst = static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD;
+          reinterpret_cast<uint2*>(dst)[hl] = lo[u];
+          reinterpret_cast<uint2*>(dst)[16 + hl] = hi[u];
+        }
+        continue;
+      }
+      // the two half-warps may still hold rows of different kinds (last q row / first k row,
+      // last k row / first v row): every decision below is per half-warp, the shuffles stay
+      // inside it
       const bool is_v = live && row >= n_qk;
       const bool is_q = live && row < p.hq;
       const bool has_w = live && !is_v && (is_q ? p.q_weight : p.k_weight) != nullptr;
-      float a[4], b[4];
-      unpack4(live ? lo[u] : make_uint2(0u, 0u), a);
-      unpack4(live ? hi[u] : make_uint2(0u, 0u), b);
-      float ss = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+      uint64_t a01 = from_bits2(live ? lo[u].x : 0u), a23 = from_bits2(live ? lo[u].y : 0u);
+      uint64_t b01 = from_bits2(live ? hi[u].x : 0u), b23 = from_bits2(live ? hi[u].y : 0u);
+      float ss;
+      {
+        uint64_t acc = mul_f32x2(a01, a01);
+        acc = fma_f32x2(a23, a23, acc);
+        acc = fma_f32x2(b01, b01, acc);
+        acc = fma_f32x2(b23, b23, acc);
+        float s0, s1;
+        unpack_f32x2(acc, s0, s1);
+        ss = s0 + s1;
+      }
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (has_w) {
         const float inv = rsqrtf(ss * (1.f / HD) + p.eps);
-        float na[4], nb[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          na[e] = a[e] * inv * (is_q ? w_lo[0][e] : w_lo[1][e]);
-          nb[e] = b[e] * inv * (is_q ? w_hi[0][e] : w_hi[1][e]);
-        }
-        // rounded as the reference's materialised norm output is
-        unpack4(pack4(na), a);
-        unpack4(pack4(nb), b);
+        const uint64_t inv2 = pack_f32x2(inv, inv);
+        // (x * inv) * w, rounded to the 16-bit type as the reference's materialised norm output is
+        a01 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(a01, inv2), is_q ? wq[0] : wk[0])));
+        a23 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(a23, inv2), is_q ? wq[1] : wk[1])));
+        b01 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(b01, inv2), is_q ? wq[2] : wk[2])));
+        b23 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(b23, inv2), is_q ? wq[3] : wk[3])));
       }
-      // rotary_dim 64: pairs (i, i+32) inside the first 64 elements; lanes hl < 8 hold the
-      // first members, hl >= 8 the second (partner lane ^ 8); the upper 64 pass through
-      float other[4];
+      if (half == 64) {
+        if (!is_v) {
+          // pairs (4hl+e, 64+4hl+e), both in this lane: a' = a cos - b sin, b' = a sin + b cos
+          const uint64_t x01 = a01, x23 = a23;
+          a01 = fma_f32x2(b01, ng01, mul_f32x2(x01, cs01));
+          a23 = fma_f32x2(b23, ng23, mul_f32x2(x23, cs23));
+          b01 = fma_f32x2(b01, cs01, mul_f32x2(x01, sn01));
+          b23 = fma_f32x2(b23, cs23, mul_f32x2(x23, sn23));
+        }
+      } else {
+        // rotary_dim 64: pairs (i, i+32) inside the first 64 elements; lanes hl < 8 hold the
+        // first members, hl >= 8 the second (partner lane ^ 8); the upper 64 pass through
+        float a[4], other[4];
+        unpack_f32x2(a01, a[0], a[1]);
+        unpack_f32x2(a23, a[2], a[3]);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) other[e] = __shfl_xor_sync(0xffffffffu, a[e], 8);
-      if (!is_v) {
-        if (half == 64) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {  // pairs (4hl+e, 64+4hl+e), both in this lane
-            const float x = a[e], y = b[e];
-            a[e] = x * cs[e] - y * sn[e];
-            b[e] = x * sn[e] + y * cs[e];
-          }
-        } else {
+        for (int e = 0; e < 4; ++e) other[e] = __shfl_xor_sync(0xffffffffu, a[e], 8);
+        if (!is_v) {
 #pragma unroll
           for (int e = 0; e < 4; ++e)
             a[e] = hl < 8 ? a[e] * cs[e] - other[e] * sn[e] : other[e] * sn[e] + a[e] * cs[e];
         }
+        a01 = pack_f32x2(a[0], a[1]);
+        a23 = pack_f32x2(a[2], a[3]);
       }
       if (!live) continue;
       T* dst;
@@ -201,8 +228,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
         dst = is_v ? static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD
                    : static_cast<T*>(p.k_cache) + slot * p.cache_stride + (row - p.hq) * HD;
       }
-      reinterpret_cast<uint2*>(dst)[hl] = is_v ? lo[u] : pack4(a);
-      reinterpret_cast<uint2*>(dst)[16 + hl] = is_v ? hi[u] : pack4(b);
+      reinterpret_cast<uint2*>(dst)[hl] = is_v ? lo[u] : make_uint2(to_bits2(a01), to_bits2(a23));
+      reinterpret_cast<uint2*>(dst)[16 + hl] = is_v ? hi[u] : make_uint2(to_bits2(b01), to_bits2(b23));
     }
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
