@@ -137,12 +137,23 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
   // Split the key range only when the query tiles fill at most half of the CTA slots: a
   // nearly full single wave beats more, shorter CTAs plus a merge pass.
   if (qtiles * hkv * 2 <= slots && visible > 0) {
-    // measured on cfg3/cfg4 and the small-chunk grid points: splits shorter than 2048 keys cost
-    // more in CTA start-up and merge traffic than they gain in balance
-    const int target = short_q ? 2 : 4;  // CTAs per slot aimed at
-    const int min_chunk = 2048;
-    int64_t chunk = (visible / batch) * (qtiles * hkv) / (static_cast<int64_t>(target) * slots);
-    if (chunk < min_chunk) chunk = min_chunk;
+    int64_t chunk;
+    if (short_q) {
+      // Bandwidth-bound shapes: one wave.  Every (sequence, head) unit is cut into as many
+      // equal pieces as the CTA slots allow for a sequence of average length (measured on
+      // the draft-block and verify configurations: 2 pieces of 2176 keys beat 3 of 1408 or
+      // 2048 + 2048 + 16, and pieces of 4224-4864 keys beat 2048 on log-uniform lengths: a
+      // second, partial wave costs more than the longer pieces).
+      const int64_t pieces = slots / (qtiles * hkv);                 // >= 2 here
+      chunk = (visible / batch + pieces - 1) / pieces;
+      if (chunk < 1024) chunk = 1024;
+    } else {
+      // measured on the small-chunk grid points: splits shorter than 2048 keys cost more in
+      // CTA start-up and merge traffic than they gain in balance
+      const int target = 4;  // CTAs per slot aimed at
+      chunk = (visible / batch) * (qtiles * hkv) / (static_cast<int64_t>(target) * slots);
+      if (chunk < 2048) chunk = 2048;
+    }
     chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
   }
