@@ -23,7 +23,8 @@ from typing import List, Optional, Sequence
 import torch
 
 from .. import _lib
-from ..kernel import gather_kv_indices, paged_decode_attention, paged_prefill_attention
+from ..kernel import (gather_kv_indices, paged_decode_attention, paged_prefill_attention,
+                      qk_norm_rope_store)
 
 MAX_KV_SPLITS = 32
 
@@ -115,6 +116,10 @@ class AttnBackend:
         self.kvcache.store_kv(k, v, batch.out_loc, layer_id)
         k_cache = self.kvcache.k_cache(layer_id)
         v_cache = self.kvcache.v_cache(layer_id)
+        return self._attend(q, k_cache, v_cache, metadata, is_cross_attention, sliding_window_size)
+
+    def _attend(self, q, k_cache, v_cache, metadata, is_cross_attention: bool,
+                sliding_window_size: int) -> torch.Tensor:
         if isinstance(metadata, PrefillMetadata):
             return paged_prefill_attention(
                 q, k_cache, v_cache, metadata.qo_indptr, metadata.kv_indptr, metadata.kv_indices,
@@ -126,6 +131,26 @@ class AttnBackend:
         return paged_decode_attention(
             q, k_cache, v_cache, metadata.kv_indptr, metadata.kv_indices, metadata.num_kv_splits,
             sm_scale=self.sm_scale, max_kv_splits=metadata.max_kv_splits)
+
+    def forward_from_projections(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layer_id: int,
+                                 batch, *, q_norm_weight, k_norm_weight, rope_base: float,
+                                 rms_norm_eps: float = 1e-6, rotary_dim: Optional[int] = None,
+                                 is_cross_attention: bool = False,
+                                 sliding_window_size: int = 0) -> torch.Tensor:
+        """``forward`` for a layer that hands over its raw projections: the per-head q/k
+        RMSNorm, the rotary embedding at ``batch.attn_metadata.positions`` and the K/V store
+        run as one pass (``qk_norm_rope_store``; q is updated in place), then paged attention.
+
+        Equivalent to the reference layer's ``q_norm``, ``k_norm``, ``rope``, ``rope`` followed by
+        ``AttnBackend.forward`` (mini_sglang_mlx/models/qwen3.py:58-68)."""
+        assert sliding_window_size >= 0, (
+            f"sliding_window_size must be >= 0, got {sliding_window_size}")
+        metadata = batch.attn_metadata
+        k_cache = self.kvcache.k_cache(layer_id)
+        v_cache = self.kvcache.v_cache(layer_id)
+        qk_norm_rope_store(q, k, v, q_norm_weight, k_norm_weight, metadata.positions, batch.out_loc,
+                           k_cache, v_cache, rope_base=rope_base, eps=rms_norm_eps, rotary_dim=rotary_dim)
+        return self._attend(q, k_cache, v_cache, metadata, is_cross_attention, sliding_window_size)
 
     def store_kv_only(self, k: torch.Tensor, v: torch.Tensor, out_loc: torch.Tensor,
                       layer_id: int) -> None:

@@ -137,23 +137,16 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
   // Split the key range only when the query tiles fill at most half of the CTA slots: a
   // nearly full single wave beats more, shorter CTAs plus a merge pass.
   if (qtiles * hkv * 2 <= slots && visible > 0) {
-    int64_t chunk;
-    if (short_q) {
-      // Bandwidth-bound shapes: one wave.  Every (sequence, head) unit is cut into as many
-      // equal pieces as the CTA slots allow for a sequence of average length (measured on
-      // the draft-block and verify configurations: 2 pieces of 2176 keys beat 3 of 1408 or
-      // 2048 + 2048 + 16, and pieces of 4224-4864 keys beat 2048 on log-uniform lengths: a
-      // second, partial wave costs more than the longer pieces).
-      const int64_t pieces = slots / (qtiles * hkv);                 // >= 2 here
-      chunk = (visible / batch + pieces - 1) / pieces;
-      if (chunk < 1024) chunk = 1024;
-    } else {
-      // measured on the small-chunk grid points: splits shorter than 2048 keys cost more in
-      // CTA start-up and merge traffic than they gain in balance
-      const int target = 4;  // CTAs per slot aimed at
-      chunk = (visible / batch) * (qtiles * hkv) / (static_cast<int64_t>(target) * slots);
-      if (chunk < 2048) chunk = 2048;
-    }
+    // One wave: every (sequence, head, query tile) unit is cut into as many equal pieces as
+    // the CTA slots allow for a sequence of average length.  Measured on the draft-block and
+    // verify configurations and on the small-chunk points of the prefill grid (chunk x prefix
+    // 128 x 32768: 9 pieces of 3712 keys 94 us against 121 us with 2048-key pieces; 256 x 8192:
+    // 4 pieces 67 us against 83; 512 x 16384: 2 pieces 172 us against 231; 16 query tokens over
+    // a 4096 window: 2 pieces of 2176 keys 88 us against 98 with 2048 + 2048 + 16): a second,
+    // partial wave and the start-up of more CTAs cost more than the longer pieces.
+    const int64_t pieces = slots / (qtiles * hkv);                 // >= 2 here
+    int64_t chunk = (visible / batch + pieces - 1) / pieces;
+    if (chunk < 1024) chunk = 1024;
     chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
   }

@@ -125,3 +125,41 @@ def test_fused_step_then_attention_equals_the_unfused_layer():
                             kcd, vcd, rope_base=1e6)
     out = paged_prefill_attention(qd, kcd, vcd, *[m.cuda() for m in meta], d ** -0.5, n)
     assert_close_to_oracle(out, ref, "fused step + prefill")
+
+
+def test_backend_forward_from_projections_equals_norm_rope_then_forward():
+    """AttnBackend.forward_from_projections (fused step + attention) against the oracle chain
+    norm -> rope -> AttnBackend.forward, for a chunked prefill with a cached prefix and a decode step."""
+    from mini_sglang_mlx_b200.attention import AttnBackend
+    from mini_sglang_mlx_b200.core import Batch, BatchPhase, Req
+    from mini_sglang_mlx_b200.kvcache import MHAKVCache
+    from oracle.qk_norm_rope_oracle import rms_norm_oracle, rope_oracle
+    from tests.helpers import assert_close_to_oracle
+
+    class Cfg:
+        head_dim, num_kv_heads, num_qo_heads = 128, 8, 32
+
+    g = torch.Generator().manual_seed(31)
+    pools = [MHAKVCache(8, 1, 128, 2049, torch.bfloat16) for _ in range(2)]
+    table = torch.randperm(2048, generator=g)[: 4 * 512].view(4, 512).int().cuda()
+    fused, plain = AttnBackend(Cfg, pools[0], table), AttnBackend(Cfg, pools[1], table)
+    qw = (1 + 0.1 * torch.randn(128, generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(128, generator=g)).bfloat16()
+    reqs = [Req(table_idx=2, cached_len=0, device_len=130), Req(table_idx=0, cached_len=0, device_len=33)]
+    for phase in (BatchPhase.PREFILL, BatchPhase.DECODE):
+        n = sum(r.extend_len for r in reqs)
+        q = (torch.randn(n, 32, 128, generator=g) * 2).bfloat16()
+        k = torch.randn(n, 8, 128, generator=g).bfloat16()
+        v = torch.randn(n, 8, 128, generator=g).bfloat16()
+        out_loc = torch.cat([table[r.table_idx, r.cached_len:r.device_len] for r in reqs])
+        batch = Batch(reqs=reqs, phase=phase, out_loc=out_loc)
+        fused.prepare_metadata(batch)
+        pos = batch.attn_metadata.positions.cpu()
+        out_f = fused.forward_from_projections(q.cuda(), k.cuda(), v.cuda(), 0, batch, q_norm_weight=qw.cuda(),
+                                               k_norm_weight=kw.cuda(), rope_base=1e6)
+        qn = rope_oracle(rms_norm_oracle(q, qw, 1e-6), pos, 1e6, 128)
+        kn = rope_oracle(rms_norm_oracle(k, kw, 1e-6), pos, 1e6, 128)
+        out_p = plain.forward(qn.cuda(), kn.cuda(), v.cuda(), 0, batch)
+        assert_close_to_oracle(out_f, out_p.float().cpu(), f"fused layer {phase}")
+        for r in reqs:
+            r.complete_one()
