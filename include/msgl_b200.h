@@ -137,7 +137,7 @@ size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, in
  * Key t of a sequence is visible to query row p iff t < kv_len and
  * (is_cross_attention or t <= prefix_len + p) and
  * (sliding_window_size == 0 or t >= prefix_len + p - sliding_window_size + 1).
- * Rows with no visible key produce zeros.
+ * Rows with no visible key produce zeros.  head_dim 128 or 256, as the reference.
  */
 int msgl_paged_prefill_attention(
     const void* q, const void* k_cache, const void* v_cache,

@@ -109,9 +109,10 @@ struct PrefillPlan {
 
 // Query blocks that fill at most one 128-row sub-tile (verify, draft blocks) run the
 // one-sub-tile shape (64-token key tiles, two CTAs per SM); longer chunks the two-sub-tile
-// shape with 128-token key tiles.
-bool prefill_short_q(int max_len_extend, int group) {
-  return static_cast<int64_t>(max_len_extend) * group <= msgl::kTcSub;
+// shape with 128-token key tiles.  head_dim 256 always runs the one-sub-tile shape (its
+// output accumulator alone takes 256 of the 512 TMEM columns), one CTA per SM.
+bool prefill_short_q(int max_len_extend, int group, int head_dim) {
+  return head_dim == 256 || static_cast<int64_t>(max_len_extend) * group <= msgl::kTcSub;
 }
 
 PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int hkv, int head_dim,
@@ -120,9 +121,11 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
   // GPU a CTA; then about two CTAs per slot are made.
   PrefillPlan pl{};
   const int G = hq / hkv;
-  const bool short_q = prefill_short_q(max_len_extend, G);
+  const bool short_q = prefill_short_q(max_len_extend, G, head_dim);
   const int BM = short_q ? msgl::TcShape<1>::kBM : msgl::TcShape<2>::kBM;
-  const int slots = sms * (short_q ? msgl::TcShape<1>::kCtasPerSm : msgl::TcShape<2>::kCtasPerSm);
+  const int slots = sms * (head_dim == 256 ? msgl::TcShape<1, 256>::kCtasPerSm
+                           : short_q       ? msgl::TcShape<1>::kCtasPerSm
+                                           : msgl::TcShape<2>::kCtasPerSm);
   int64_t qtiles = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, 0);
   {  // the other upper bound on the number of query tiles: every sequence at the longest length
     const int64_t per_seq = (static_cast<int64_t>(max_len_extend) * G + BM - 1) / BM;
@@ -356,9 +359,6 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
   if (batch <= 0) return fail(MSGL_BAD_SHAPE, std::string(op) + "batch must be > 0");
   if (dtype != MSGL_DTYPE_BF16 && dtype != MSGL_DTYPE_F16)
     return fail(MSGL_BAD_DTYPE, std::string(op) + "unsupported dtype, must be float16 or bfloat16");
-  if (head_dim != 128)
-    return fail(MSGL_UNSUPPORTED_HEAD_DIM,
-                std::string(op) + "head_dim 256 is not built in this library");
   if (total_q == 0) return MSGL_OK;
   if (num_kv_heads > 65535)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "num_kv_heads must be <= 65535");
@@ -405,18 +405,25 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
 
   dim3 grid(static_cast<unsigned>(pl.items * num_kv_heads));
   dim3 mgrid(total_q, num_q_heads);
-  const bool short_q = prefill_short_q(max_len_extend, p.group);
+  const bool short_q = prefill_short_q(max_len_extend, p.group, head_dim);
   cudaError_t e;
   auto launch = [&](auto kernel, auto merge, int threads, int smem) -> cudaError_t {
     cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
     kernel<<<grid, threads, smem, s>>>(p);
-    if (pl.kv_chunk > 0) return launch_dependent(merge, mgrid, dim3(128), s, p);
+    if (pl.kv_chunk > 0) return launch_dependent(merge, mgrid, dim3(head_dim), s, p);
     return cudaSuccess;
   };
   using S1 = msgl::TcShape<1>;
   using S2 = msgl::TcShape<2>;
-  if (dtype == MSGL_DTYPE_BF16) {
+  using S1w = msgl::TcShape<1, 256>;
+  if (head_dim == 256) {
+    e = dtype == MSGL_DTYPE_BF16
+            ? launch(msgl::prefill_tc_kernel<__nv_bfloat16, 64, 1, 256>,
+                     msgl::prefill_merge_kernel<__nv_bfloat16, 256, S1w::kBM>, S1w::kThreads, S1w::kSmemBytes)
+            : launch(msgl::prefill_tc_kernel<__half, 64, 1, 256>,
+                     msgl::prefill_merge_kernel<__half, 256, S1w::kBM>, S1w::kThreads, S1w::kSmemBytes);
+  } else if (dtype == MSGL_DTYPE_BF16) {
     using T = __nv_bfloat16;
     e = short_q ? launch(msgl::prefill_tc_kernel<T, 64, 1>, msgl::prefill_merge_kernel<T, 128, S1::kBM>,
                          S1::kThreads, S1::kSmemBytes)

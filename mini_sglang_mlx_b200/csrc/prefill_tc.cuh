@@ -45,23 +45,28 @@
 namespace msgl {
 
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
-constexpr int kTcQTileBytes = 128 * 256;                     // one 128-row query sub-tile
 
 // Shape of a CTA.  NSUB = 2: 256 query rows, 16 warps, all 512 TMEM columns, 160 KB K/V
 // ring, one CTA per SM.  NSUB = 1: 128 rows, 12 warps, 256 TMEM columns, 64 KB ring, two
 // CTAs per SM (short query blocks are bandwidth-bound: two independent pipelines per SM
 // keep more copies in flight).
-template <int NSUB>
+template <int NSUB, int HD = 128>
 struct TcShape {
+  static_assert(HD == 128 || (HD == 256 && NSUB == 1), "head_dim 256 runs the one-sub-tile shape");
   static constexpr int kBM = NSUB * kTcSub;                       // packed query rows per CTA
+  static constexpr int kRowBytes = HD * 2;                        // one token row of one head
+  static constexpr int kQTileBytes = kTcSub * kRowBytes;          // one 128-row query sub-tile
   static constexpr int kWarps = NSUB == 2 ? 16 : 12;
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kMmaWarp = 4 * NSUB;                       // after the softmax warps
   static constexpr int kProducerWarp0 = kMmaWarp + 1;             // ... the rest copy
-  static constexpr int kRingBytes = NSUB == 2 ? 5 * 128 * 256 : 4 * 64 * 256;
-  static constexpr int kSmemBytes = NSUB * kTcQTileBytes + kRingBytes + 1024;  // + alignment slack
-  static constexpr int kTmemCols = NSUB * 256;
-  static constexpr int kCtasPerSm = NSUB == 2 ? 1 : 2;
+  static constexpr int kRingBytes = NSUB == 2 ? 5 * 128 * 256 : 4 * 64 * kRowBytes;
+  static constexpr int kSmemBytes = NSUB * kQTileBytes + kRingBytes + 1024;  // + alignment slack
+  static constexpr int kTmemCols = HD == 256 ? 512 : NSUB * 256;  // S buffers + O (HD columns per sub-tile)
+  static constexpr int kCtasPerSm = (NSUB == 2 || HD == 256) ? 1 : 2;
+  // register cap at launch: the one-sub-tile shapes start at 80 registers either way (the
+  // setmaxnreg budgets below are written against that pool)
+  static constexpr int kMinCtasForRegs = NSUB == 2 ? 1 : 2;
 };
 constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
 
@@ -291,21 +296,22 @@ struct TcBarriers {
   uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];
 };
 
-template <typename T, int BN, int NSUB>
-__global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasPerSm)
+template <typename T, int BN, int NSUB, int HD = 128>
+__global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>::kMinCtasForRegs)
     prefill_tc_kernel(const PrefillParams p) {
   static_assert(BN == 64 || BN == 128, "key tile of 64 or 128 tokens");
   static_assert(NSUB == 2 || BN == 64, "the one-sub-tile shape has TMEM for 64-column score tiles only");
-  using Shape = TcShape<NSUB>;
-  constexpr int HD = 128;
+  using Shape = TcShape<NSUB, HD>;
+  constexpr int kTcQTileBytes = Shape::kQTileBytes;
+  constexpr int CPR = HD / 8;                          // 16-byte chunks of a token row
   constexpr int BM = Shape::kBM, SUB = kTcSub;
   constexpr int kTcThreads = Shape::kThreads;
   constexpr int kMmaWarp = Shape::kMmaWarp;
   constexpr int kTcProducerWarp0 = Shape::kProducerWarp0;
   constexpr int NPROD = (Shape::kWarps - kTcProducerWarp0) * 32;  // producer threads
-  constexpr int PROWS = NPROD / 16;                     // token rows covered by one pass of the producers
+  constexpr int PROWS = NPROD / CPR;                    // token rows covered by one pass of the producers
   constexpr int LA = BN == 64 ? 2 : 1;        // key tiles S runs ahead of PV (= S buffers per sub-tile)
-  constexpr int kTcKvTileBytes = BN * 256;
+  constexpr int kTcKvTileBytes = BN * Shape::kRowBytes;
   constexpr int kTcBufs = Shape::kRingBytes / kTcKvTileBytes;
   constexpr uint32_t kOCol = NSUB * 128;      // first TMEM column of the O accumulators
 
@@ -402,8 +408,8 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
   if (warp >= kTcProducerWarp0) {
     // =========================================================== producers
     const int ptid = tid - kTcProducerWarp0 * 32;  // 0..NPROD-1
-    const int chunk = ptid & 15;           // 16-byte chunk of a 256-byte row
-    const int rsub = ptid >> 4;            // row inside a pass of PROWS rows
+    const int chunk = ptid % CPR;          // 16-byte chunk of a token row
+    const int rsub = ptid / CPR;           // row inside a pass of PROWS rows
     const T* __restrict__ q = static_cast<const T*>(p.q);
     const unsigned char* __restrict__ kbase = static_cast<const unsigned char*>(p.k_cache);
     const unsigned char* __restrict__ vbase = static_cast<const unsigned char*>(p.v_cache);
@@ -505,7 +511,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     // one elected lane in one go, each group followed by its commit.
     auto issue_step = [&](int i, bool do_pv, int t_pv, int buf_v, bool do_s, int t_s, int buf_k) {
       const uint32_t vb = (ring + buf_v * kTcKvTileBytes) >> 4;
-      const uint32_t o_tm = tmem_u + kOCol + i * 128;
+      const uint32_t o_tm = tmem_u + kOCol + i * HD;
       const uint32_t p_tm = tmem_u + i * 128 + (t_pv % LA) * BN;
       const uint32_t qa = (q_smem + i * kTcQTileBytes) >> 4;
       const uint32_t kb = (ring + buf_k * kTcKvTileBytes) >> 4;
@@ -523,9 +529,9 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
           tc_commit(bar_o);
         }
         if (do_s) {
-          // S_i[t] = Q_i K_t^T : 8 k-steps of 16 elements; both operands K-major
+          // S_i[t] = Q_i K_t^T : HD/16 k-steps of 16 elements; both operands K-major
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
+          for (int ks = 0; ks < HD / 16; ++ks) {
             const uint32_t qoff = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;
             const uint32_t koff = ((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4;
             tc_mma_ss(s_tm, desc_hi_k | (qa + qoff), desc_hi_k | (kb + koff), idesc_s,
@@ -594,7 +600,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     const int r = tid & 127;                 // row inside the sub-tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_tm = tmem + lane_base + i * 128;
-    const uint32_t o_tm = tmem + lane_base + kOCol + i * 128;
+    const uint32_t o_tm = tmem + lane_base + kOCol + i * HD;
     const int row = i * SUB + r;
     const int pk = pk0 + row;
     const int tl = pk / G;
@@ -660,7 +666,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(o_tm + c * 32, o);
           tmem_wait_ld();
@@ -713,12 +719,14 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
     if (alive) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       if (p.kv_chunk == 0) {
-        // Each warp stages its 32 output rows (256 bytes each) in the Q sub-tile's shared memory,
-        // free once the last S MMA has completed, then writes them out two whole rows per
-        // instruction; chunk c of row r sits at chunk position c ^ (r & 15) (conflict-free).
+        // Each warp stages its 32 output rows (HD*2 bytes each) in the Q sub-tile's shared memory,
+        // free once the last S MMA has completed, then writes them out as whole rows (two per
+        // instruction at head_dim 128); chunk c of row r sits at chunk position c ^ (r & 15)
+        // (conflict-free).
+        constexpr int RB = HD * 2;
         unsigned char* stage = smem_raw + (smem0 - smem_u32(smem_raw)) + i * kTcQTileBytes;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t v[32];
           if (my_tiles > 0) {
             tmem_ld32(o_tm + c * 32, v);
@@ -736,15 +744,15 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
             w.z = MmaOp<T>::pack(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
             w.w = MmaOp<T>::pack(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
             const int chunk = c * 4 + (e >> 3);
-            *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = w;
+            *reinterpret_cast<uint4*>(stage + r * RB + ((chunk ^ (r & 15)) << 4)) = w;
           }
         }
         __syncwarp();
         {
           const int wrow0 = (warp & 3) * 32;   // first row of this warp inside the sub-tile
-          const int chunk = lane & 15;
+          const int chunk = lane % CPR;
 #pragma unroll 4
-          for (int rr = lane >> 4; rr < 32; rr += 2) {
+          for (int rr = lane / CPR; rr < 32; rr += 32 / CPR) {
             const int rloc = wrow0 + rr;
             const int prow = i * SUB + rloc;
             if (prow < rows_valid) {
@@ -753,7 +761,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
               T* dst = static_cast<T*>(p.out) +
                        (static_cast<int64_t>(sq.q_begin + tlr) * p.hq + static_cast<int64_t>(h) * G + gr) * HD;
               const uint4 w =
-                  *reinterpret_cast<const uint4*>(stage + rloc * 256 + ((chunk ^ (rloc & 15)) << 4));
+                  *reinterpret_cast<const uint4*>(stage + rloc * RB + ((chunk ^ (rloc & 15)) << 4));
               *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(dst) + chunk * 16) = w;
             }
           }
@@ -767,7 +775,7 @@ __global__ void __launch_bounds__(TcShape<NSUB>::kThreads, TcShape<NSUB>::kCtasP
               make_float2(my_tiles > 0 ? m_ref : -INFINITY, my_tiles > 0 ? l : 0.f);
         }
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t v[32];
           if (my_tiles > 0) {
             tmem_ld32(o_tm + c * 32, v);

@@ -182,3 +182,36 @@ def test_cfg5b_points(chunk, prefix):
     from mini_sglang_mlx_b200 import synthetic as S
     w = S.cfg5b_prefill_point(chunk, prefix)
     assert_close_to_oracle(_run_workload(w), _oracle_workload(w), f"cfg5b {chunk}x{prefix}")
+
+
+# ---------------------------------------------------------------- head_dim 256
+# (the reference's prefill op accepts 128 and 256: csrc/paged_prefill_attention.cpp:53-56)
+@pytest.mark.parametrize("hkv,hq", [(2, 8), (4, 16), (1, 1), (2, 16)])
+@pytest.mark.parametrize("q_lens,prefixes", [([1], [0]), ([237], [0]), ([64], [700]), ([300, 17, 128], [100, 2000, 0]),
+                                            ([1024], [512])])
+def test_head_dim_256(hkv, hq, q_lens, prefixes):
+    d = make_inputs(q_lens, prefixes, hkv, hq, seed=sum(q_lens) + hq, d=256)
+    assert_close_to_oracle(run(d), oracle(d), f"D=256 q{q_lens} prefix{prefixes} Hkv{hkv}/Hq{hq}")
+
+
+@pytest.mark.parametrize("cross,window", [(False, 0), (True, 0), (False, 64), (True, 64), (False, 1)])
+def test_head_dim_256_mask_modes(cross, window):
+    d = make_inputs([16, 8, 1, 200], [500, 77, 130, 0], 2, 8, seed=3, d=256)
+    assert_close_to_oracle(run(d, cross, window), oracle(d, cross, window), f"D=256 cross={cross} W={window}")
+
+
+def test_head_dim_256_long_keys_take_the_split_path_and_f16():
+    d = make_inputs([8, 8], [9000, 3000], 2, 16, seed=5, d=256)          # few query tiles: key range is split
+    assert_close_to_oracle(run(d), oracle(d), "D=256 verify shape")
+    d = make_inputs([130], [260], 4, 16, seed=6, d=256, dtype=torch.float16)
+    assert_close_to_oracle(run(d), oracle(d), "D=256 f16")
+
+
+def test_head_dim_256_one_query_token_equals_the_decode_op():
+    from mini_sglang_mlx_b200 import paged_decode_attention
+    d = make_inputs([1, 1, 1], [1500, 63, 4097], 4, 16, seed=8, d=256)
+    out_p = run(d)
+    splits = torch.tensor([4, 1, 8], dtype=torch.int32).cuda()
+    out_d = paged_decode_attention(d["q"], d["k_cache"], d["v_cache"], d["kv_indptr"], d["kv_indices"], splits,
+                                   1 / math.sqrt(256), 8)
+    assert (out_p.float() - out_d.float()).abs().max().item() <= 2e-2
