@@ -117,6 +117,20 @@ int msgl_paged_decode_attention_static(
     int dtype, float sm_scale, int max_kv_splits, void* stream);
 
 /*
+ * msgl_paged_decode_attention with the output gate of the reference's Qwen3.5 attention
+ * layer fused into the final write: out = attention * sigmoid(gate), gate (batch,
+ * num_q_heads, head_dim) in the data dtype, both factors rounded to that dtype before the
+ * product as the reference's array ops do (mini_sglang_mlx/models/qwen3_5.py:91-110).
+ * No operator of the reference does this (the gate is an array op after its kernel).
+ */
+int msgl_paged_decode_attention_gated(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* num_kv_splits,
+    const void* gate, void* out, void* workspace, size_t workspace_bytes,
+    int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t num_slots,
+    int dtype, float sm_scale, int max_kv_splits, void* stream);
+
+/*
  * Bytes of scratch the prefill op needs for the given problem (split-KV
  * partials when there are too few query tiles to fill the GPU, plus a small
  * planning area).  total_kv = kv_indptr[batch] = length of kv_indices.
@@ -143,6 +157,18 @@ int msgl_paged_prefill_attention(
     const void* q, const void* k_cache, const void* v_cache,
     const int32_t* qo_indptr, const int32_t* kv_indptr, const int32_t* kv_indices,
     const int32_t* prefix_lens, void* out, void* workspace, size_t workspace_bytes,
+    int batch, int total_q, int64_t total_kv, int num_q_heads, int num_kv_heads, int head_dim,
+    int64_t num_slots, int dtype, float sm_scale, int max_len_extend,
+    int is_cross_attention, int sliding_window_size, void* stream);
+
+/*
+ * msgl_paged_prefill_attention with out = attention * sigmoid(gate) fused into the final
+ * write (see msgl_paged_decode_attention_gated); gate (total_q_tokens, num_q_heads, head_dim).
+ */
+int msgl_paged_prefill_attention_gated(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* qo_indptr, const int32_t* kv_indptr, const int32_t* kv_indices,
+    const int32_t* prefix_lens, const void* gate, void* out, void* workspace, size_t workspace_bytes,
     int batch, int total_q, int64_t total_kv, int num_q_heads, int num_kv_heads, int head_dim,
     int64_t num_slots, int dtype, float sm_scale, int max_len_extend,
     int is_cross_attention, int sliding_window_size, void* stream);
@@ -193,9 +219,10 @@ int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64
  * mini_sglang_mlx/models/qwen3.py:58-68 (q_norm, k_norm, rope, rope) plus the
  * store_kv_cache call of attention/backend.py:117-121; the reference has no fused
  * operator of this kind (its extension stops at store_kv_cache).
- * q (n_tokens, Hq, 128), k and v (n_tokens, Hkv, 128) with the given token strides in
- * elements (rows of a fused qkv projection are fine); caches (num_slots, Hkv, 128) with
- * cache_row_stride elements per slot.  head_dim must be 128, rotary_dim 64 or 128.
+ * q (n_tokens, Hq, D), k and v (n_tokens, Hkv, D) with the given token strides in
+ * elements (rows of a fused qkv projection are fine); caches (num_slots, Hkv, D) with
+ * cache_row_stride elements per slot.  head_dim 128 or 256; rotary_dim = head_dim, head_dim/2
+ * or head_dim/4 (the first rotary_dim elements of a head are rotated, the rest pass through).
  * Tokens whose out_loc is outside [0, num_slots) get their q processed and their k/v dropped.
  */
 int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q_weight,

@@ -27,6 +27,11 @@ SIGNATURES = {
     "msgl_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "msgl_paged_decode_attention": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i64, _i, _f, _i, _vp]),
+    "msgl_paged_decode_attention_gated": (
+        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i64, _i, _f, _i, _vp]),
+    "msgl_paged_prefill_attention_gated": (
+        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i64, _i, _i, _i, _i64,
+             _i, _f, _i, _i, _i, _vp]),
     "msgl_paged_decode_attention_static": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _f, _i, _vp]),
     "msgl_prefill_workspace_bytes": (_sz, [_i, _i, _i64, _i, _i, _i, _i, _i]),

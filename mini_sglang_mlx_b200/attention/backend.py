@@ -103,12 +103,16 @@ class AttnBackend:
 
     # ------------------------------------------------------------------ forward
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layer_id: int, batch, *,
-                is_cross_attention: bool = False, sliding_window_size: int = 0) -> torch.Tensor:
+                is_cross_attention: bool = False, sliding_window_size: int = 0,
+                gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Write this step's K/V rows at ``batch.out_loc`` and run paged attention.
 
         q ``[N, Hq, D]``, k/v ``[N, Hkv, D]``.  The mask flags compose as in the
         reference (lines 97-132): causal / full / causal+window /
-        bidirectional+window; the decode path accepts neither.
+        bidirectional+window; the decode path accepts neither.  ``gate`` (same shape as
+        q, an addition to the reference signature): the result is multiplied by
+        ``sigmoid(gate)`` in the kernel's final write (the reference's Qwen3.5 layer does it
+        as an array op afterwards, models/qwen3_5.py:110).
         """
         assert sliding_window_size >= 0, (
             f"sliding_window_size must be >= 0, got {sliding_window_size}")
@@ -116,27 +120,27 @@ class AttnBackend:
         self.kvcache.store_kv(k, v, batch.out_loc, layer_id)
         k_cache = self.kvcache.k_cache(layer_id)
         v_cache = self.kvcache.v_cache(layer_id)
-        return self._attend(q, k_cache, v_cache, metadata, is_cross_attention, sliding_window_size)
+        return self._attend(q, k_cache, v_cache, metadata, is_cross_attention, sliding_window_size, gate)
 
     def _attend(self, q, k_cache, v_cache, metadata, is_cross_attention: bool,
-                sliding_window_size: int) -> torch.Tensor:
+                sliding_window_size: int, gate=None) -> torch.Tensor:
         if isinstance(metadata, PrefillMetadata):
             return paged_prefill_attention(
                 q, k_cache, v_cache, metadata.qo_indptr, metadata.kv_indptr, metadata.kv_indices,
                 metadata.prefix_lens, sm_scale=self.sm_scale, max_len_extend=metadata.max_len_extend,
-                is_cross_attention=is_cross_attention, sliding_window_size=sliding_window_size)
+                is_cross_attention=is_cross_attention, sliding_window_size=sliding_window_size, gate=gate)
         assert isinstance(metadata, DecodeMetadata)
         assert not is_cross_attention and sliding_window_size == 0, (
             "is_cross_attention / sliding_window_size are only supported on the prefill path.")
         return paged_decode_attention(
             q, k_cache, v_cache, metadata.kv_indptr, metadata.kv_indices, metadata.num_kv_splits,
-            sm_scale=self.sm_scale, max_kv_splits=metadata.max_kv_splits)
+            sm_scale=self.sm_scale, max_kv_splits=metadata.max_kv_splits, gate=gate)
 
     def forward_from_projections(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layer_id: int,
                                  batch, *, q_norm_weight, k_norm_weight, rope_base: float,
                                  rms_norm_eps: float = 1e-6, rotary_dim: Optional[int] = None,
-                                 is_cross_attention: bool = False,
-                                 sliding_window_size: int = 0) -> torch.Tensor:
+                                 is_cross_attention: bool = False, sliding_window_size: int = 0,
+                                 gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``forward`` for a layer that hands over its raw projections: the per-head q/k
         RMSNorm, the rotary embedding at ``batch.attn_metadata.positions`` and the K/V store
         run as one pass (``qk_norm_rope_store``; q is updated in place), then paged attention.
@@ -150,7 +154,7 @@ class AttnBackend:
         v_cache = self.kvcache.v_cache(layer_id)
         qk_norm_rope_store(q, k, v, q_norm_weight, k_norm_weight, metadata.positions, batch.out_loc,
                            k_cache, v_cache, rope_base=rope_base, eps=rms_norm_eps, rotary_dim=rotary_dim)
-        return self._attend(q, k_cache, v_cache, metadata, is_cross_attention, sliding_window_size)
+        return self._attend(q, k_cache, v_cache, metadata, is_cross_attention, sliding_window_size, gate)
 
     def store_kv_only(self, k: torch.Tensor, v: torch.Tensor, out_loc: torch.Tensor,
                       layer_id: int) -> None:

@@ -243,12 +243,12 @@ size_t msgl_decode_workspace_bytes(int batch, int num_q_heads, int head_dim, int
   return kStatusBytes + rows * head_dim * sizeof(float) + rows * sizeof(float);
 }
 
-int msgl_paged_decode_attention(const void* q, const void* k_cache, const void* v_cache,
-                                const int32_t* kv_indptr, const int32_t* kv_indices,
-                                const int32_t* num_kv_splits, void* out, void* workspace,
-                                size_t workspace_bytes, int batch, int num_q_heads,
-                                int num_kv_heads, int head_dim, int64_t num_slots, int dtype,
-                                float sm_scale, int max_kv_splits, void* stream) {
+static int decode_impl(const void* q, const void* k_cache, const void* v_cache,
+                       const int32_t* kv_indptr, const int32_t* kv_indices,
+                       const int32_t* num_kv_splits, const void* gate, void* out, void* workspace,
+                       size_t workspace_bytes, int batch, int num_q_heads, int num_kv_heads,
+                       int head_dim, int64_t num_slots, int dtype, float sm_scale,
+                       int max_kv_splits, void* stream) {
   const char* op = "paged_decode_attention: ";
   if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "q must be 3D (batch, num_q_heads, head_dim)");
@@ -279,6 +279,7 @@ int msgl_paged_decode_attention(const void* q, const void* k_cache, const void* 
   p.kv_indices = kv_indices;
   p.num_kv_splits = num_kv_splits;
   p.out = out;
+  p.gate = gate;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   p.status = reinterpret_cast<int*>(ws);
   p.part_o = reinterpret_cast<float*>(ws + kStatusBytes);
@@ -293,6 +294,30 @@ int msgl_paged_decode_attention(const void* q, const void* k_cache, const void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == MSGL_DTYPE_BF16) return launch_decode<__nv_bfloat16>(p, head_dim, s);
   return launch_decode<__half>(p, head_dim, s);
+}
+
+int msgl_paged_decode_attention(const void* q, const void* k_cache, const void* v_cache,
+                                const int32_t* kv_indptr, const int32_t* kv_indices,
+                                const int32_t* num_kv_splits, void* out, void* workspace,
+                                size_t workspace_bytes, int batch, int num_q_heads,
+                                int num_kv_heads, int head_dim, int64_t num_slots, int dtype,
+                                float sm_scale, int max_kv_splits, void* stream) {
+  return decode_impl(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, nullptr, out, workspace,
+                     workspace_bytes, batch, num_q_heads, num_kv_heads, head_dim, num_slots, dtype,
+                     sm_scale, max_kv_splits, stream);
+}
+
+int msgl_paged_decode_attention_gated(const void* q, const void* k_cache, const void* v_cache,
+                                      const int32_t* kv_indptr, const int32_t* kv_indices,
+                                      const int32_t* num_kv_splits, const void* gate, void* out,
+                                      void* workspace, size_t workspace_bytes, int batch,
+                                      int num_q_heads, int num_kv_heads, int head_dim,
+                                      int64_t num_slots, int dtype, float sm_scale,
+                                      int max_kv_splits, void* stream) {
+  if (!gate && batch > 0) return fail(MSGL_BAD_ARG, "paged_decode_attention: null gate pointer");
+  return decode_impl(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, gate, out, workspace,
+                     workspace_bytes, batch, num_q_heads, num_kv_heads, head_dim, num_slots, dtype,
+                     sm_scale, max_kv_splits, stream);
 }
 
 int msgl_paged_decode_attention_static(const void* q, const void* k_cache, const void* v_cache,
@@ -338,14 +363,13 @@ size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, in
   return kStatusBytes + pl.plan_bytes + pl.part_ml_bytes + pl.part_o_bytes;
 }
 
-int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
-                                 const int32_t* qo_indptr, const int32_t* kv_indptr,
-                                 const int32_t* kv_indices, const int32_t* prefix_lens, void* out,
-                                 void* workspace, size_t workspace_bytes, int batch, int total_q,
-                                 int64_t total_kv, int num_q_heads, int num_kv_heads,
-                                 int head_dim, int64_t num_slots, int dtype, float sm_scale,
-                                 int max_len_extend, int is_cross_attention,
-                                 int sliding_window_size, void* stream) {
+static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
+                        const int32_t* qo_indptr, const int32_t* kv_indptr,
+                        const int32_t* kv_indices, const int32_t* prefix_lens, const void* gate,
+                        void* out, void* workspace, size_t workspace_bytes, int batch, int total_q,
+                        int64_t total_kv, int num_q_heads, int num_kv_heads, int head_dim,
+                        int64_t num_slots, int dtype, float sm_scale, int max_len_extend,
+                        int is_cross_attention, int sliding_window_size, void* stream) {
   const char* op = "paged_prefill_attention: ";
   if (total_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0 || total_kv < 0)
     return fail(MSGL_BAD_SHAPE,
@@ -384,6 +408,7 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
   p.kv_indices = kv_indices;
   p.prefix_lens = prefix_lens;
   p.out = out;
+  p.gate = gate;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   p.status = reinterpret_cast<int*>(ws);
   if (pl.kv_chunk > 0) {
@@ -439,6 +464,36 @@ int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void*
   if (e != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   return MSGL_OK;
+}
+
+int msgl_paged_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
+                                 const int32_t* qo_indptr, const int32_t* kv_indptr,
+                                 const int32_t* kv_indices, const int32_t* prefix_lens, void* out,
+                                 void* workspace, size_t workspace_bytes, int batch, int total_q,
+                                 int64_t total_kv, int num_q_heads, int num_kv_heads,
+                                 int head_dim, int64_t num_slots, int dtype, float sm_scale,
+                                 int max_len_extend, int is_cross_attention,
+                                 int sliding_window_size, void* stream) {
+  return prefill_impl(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens, nullptr, out,
+                      workspace, workspace_bytes, batch, total_q, total_kv, num_q_heads, num_kv_heads,
+                      head_dim, num_slots, dtype, sm_scale, max_len_extend, is_cross_attention,
+                      sliding_window_size, stream);
+}
+
+int msgl_paged_prefill_attention_gated(const void* q, const void* k_cache, const void* v_cache,
+                                       const int32_t* qo_indptr, const int32_t* kv_indptr,
+                                       const int32_t* kv_indices, const int32_t* prefix_lens,
+                                       const void* gate, void* out, void* workspace,
+                                       size_t workspace_bytes, int batch, int total_q,
+                                       int64_t total_kv, int num_q_heads, int num_kv_heads,
+                                       int head_dim, int64_t num_slots, int dtype, float sm_scale,
+                                       int max_len_extend, int is_cross_attention,
+                                       int sliding_window_size, void* stream) {
+  if (!gate && total_q > 0) return fail(MSGL_BAD_ARG, "paged_prefill_attention: null gate pointer");
+  return prefill_impl(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens, gate, out,
+                      workspace, workspace_bytes, batch, total_q, total_kv, num_q_heads, num_kv_heads,
+                      head_dim, num_slots, dtype, sm_scale, max_len_extend, is_cross_attention,
+                      sliding_window_size, stream);
 }
 
 int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, const void* k,
@@ -503,10 +558,11 @@ int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q
   if (n_tokens < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0)
     return fail(MSGL_BAD_SHAPE, std::string(op) +
                 "q must be (n_tokens, num_q_heads, head_dim), k and v (n_tokens, num_kv_heads, head_dim)");
-  if (head_dim != 128)
-    return fail(MSGL_UNSUPPORTED_HEAD_DIM, std::string(op) + "head_dim must be 128");
-  if (rotary_dim != 64 && rotary_dim != 128)
-    return fail(MSGL_BAD_ARG, std::string(op) + "rotary_dim must be 64 or 128");
+  if (head_dim != 128 && head_dim != 256)
+    return fail(MSGL_UNSUPPORTED_HEAD_DIM, std::string(op) + "head_dim must be 128 or 256");
+  if (rotary_dim != head_dim && rotary_dim != head_dim / 2 && rotary_dim != head_dim / 4)
+    return fail(MSGL_BAD_ARG,
+                std::string(op) + "rotary_dim must be head_dim, head_dim/2 or head_dim/4");
   if (dtype != MSGL_DTYPE_BF16 && dtype != MSGL_DTYPE_F16)
     return fail(MSGL_BAD_DTYPE, std::string(op) + "q, k, v, the weights and the caches must be bf16 or f16");
   if (!(rope_base > 1.f) || !(eps >= 0.f))
@@ -518,11 +574,14 @@ int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q
   if (n_tokens == 0) return MSGL_OK;
   if (!q || !k || !v || !positions || !out_loc || !k_cache || !v_cache)
     return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
-  auto aligned8 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 8 == 0; };
-  if (!aligned8(q) || !aligned8(k) || !aligned8(v) || !aligned8(k_cache) || !aligned8(v_cache) ||
-      q_token_stride % 4 != 0 || k_token_stride % 4 != 0 || v_token_stride % 4 != 0 ||
-      cache_row_stride % 4 != 0)
-    return fail(MSGL_BAD_ARG, std::string(op) + "q, k, v and cache rows must be 8-byte aligned");
+  const int va = head_dim == 256 ? 16 : 8;   // bytes of one lane's access
+  auto aligned = [va](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % va == 0; };
+  const int64_t ve = va / 2;
+  if (!aligned(q) || !aligned(k) || !aligned(v) || !aligned(k_cache) || !aligned(v_cache) ||
+      q_token_stride % ve != 0 || k_token_stride % ve != 0 || v_token_stride % ve != 0 ||
+      cache_row_stride % ve != 0)
+    return fail(MSGL_BAD_ARG, std::string(op) + "q, k, v and cache rows must be 8-byte aligned "
+                                                "(16-byte at head_dim 256)");
   msgl::QkNormRopeParams p{};
   p.q = q;
   p.k = k;
@@ -546,12 +605,19 @@ int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q
   p.eps = eps;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int rows = num_q_heads + 2 * num_kv_heads;
-  int threads = 32 * ((rows + 15) / 16);   // a warp per sixteen rows: two passes of eight
+  const int per_warp = head_dim == 256 ? 8 : 16;   // rows of a warp: two passes of four or eight
+  int threads = 32 * ((rows + per_warp - 1) / per_warp);
   if (threads > 256) threads = 256;
-  if (dtype == MSGL_DTYPE_BF16)
-    msgl::qk_norm_rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(p);
-  else
-    msgl::qk_norm_rope_store_kernel<__half><<<n_tokens, threads, 0, s>>>(p);
+  if (head_dim == 256) {
+    if (dtype == MSGL_DTYPE_BF16)
+      msgl::qk_norm_rope_store_kernel<__nv_bfloat16, 256><<<n_tokens, threads, 0, s>>>(p);
+    else
+      msgl::qk_norm_rope_store_kernel<__half, 256><<<n_tokens, threads, 0, s>>>(p);
+  } else if (dtype == MSGL_DTYPE_BF16) {
+    msgl::qk_norm_rope_store_kernel<__nv_bfloat16, 128><<<n_tokens, threads, 0, s>>>(p);
+  } else {
+    msgl::qk_norm_rope_store_kernel<__half, 128><<<n_tokens, threads, 0, s>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("qk_norm_rope_store", e);
   return MSGL_OK;

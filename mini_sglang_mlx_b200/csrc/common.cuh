@@ -124,6 +124,23 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <>
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+
+// out * sigmoid(gate) as the reference's layer computes it after the attention op
+// (mini_sglang_mlx/models/qwen3_5.py:110): the attention output and the sigmoid are arrays of
+// the 16-bit type, so each is rounded before the product is.
+template <typename T>
+__device__ __forceinline__ T apply_gate(float out, T gate) {
+  const float o = to_f32(MmaOp<T>::from_float(out));
+  const float s = to_f32(MmaOp<T>::from_float(1.f / (1.f + __expf(-to_f32(gate)))));
+  return MmaOp<T>::from_float(o * s);
+}
+
 // Reduce over the four lanes that share a row of an m16n8 accumulator.
 __device__ __forceinline__ float quad_max(float v) {
   v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));

@@ -33,6 +33,7 @@ struct DecodeParams {
   const int32_t* kv_indices;
   const int32_t* num_kv_splits;  // may be null
   void* out;
+  const void* gate;  // (batch, hq, D) or null: out *= sigmoid(gate)
   float* part_o;    // (batch, hq, max_splits, D)
   float* part_lse;  // (batch, hq, max_splits)
   int* status;      // device status word (0 = ok); may be null
@@ -293,7 +294,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
       for (int w = 0; w < NWARPS; ++w) num += wgt[w] * sm_o[(w * 16 + g) * HD + d];
       const float val = num * inv;
       if (splits == 1) {
-        out[hq_idx * HD + d] = MmaOp<T>::from_float(val);
+        out[hq_idx * HD + d] = p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[hq_idx * HD + d])
+                                      : MmaOp<T>::from_float(val);
       } else {
         p.part_o[(hq_idx * p.max_splits + split) * HD + d] = val;
       }
@@ -327,7 +329,9 @@ __global__ void __launch_bounds__(HD) decode_merge_kernel(const DecodeParams p) 
       num += w * po[s * HD + d];
     }
   }
-  static_cast<T*>(p.out)[hq_idx * HD + d] = MmaOp<T>::from_float(den > 0.f ? num / den : 0.f);
+  const float val = den > 0.f ? num / den : 0.f;
+  static_cast<T*>(p.out)[hq_idx * HD + d] =
+      p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[hq_idx * HD + d]) : MmaOp<T>::from_float(val);
 }
 
 }  // namespace msgl

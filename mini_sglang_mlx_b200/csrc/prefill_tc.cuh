@@ -760,8 +760,17 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
               const int tlr = pkr / G, gr = pkr - tlr * G;
               T* dst = static_cast<T*>(p.out) +
                        (static_cast<int64_t>(sq.q_begin + tlr) * p.hq + static_cast<int64_t>(h) * G + gr) * HD;
-              const uint4 w =
+              uint4 w =
                   *reinterpret_cast<const uint4*>(stage + rloc * RB + ((chunk ^ (rloc & 15)) << 4));
+              if (p.gate) {
+                const T* grow = static_cast<const T*>(p.gate) + (dst - static_cast<T*>(p.out));
+                const uint4 gv = *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const unsigned char*>(grow) + chunk * 16);
+                T* wo = reinterpret_cast<T*>(&w);
+                const T* wg = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) wo[e] = apply_gate<T>(to_f32(wo[e]), wg[e]);
+              }
               *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(dst) + chunk * 16) = w;
             }
           }
@@ -842,8 +851,10 @@ __global__ void __launch_bounds__(HD) prefill_merge_kernel(const PrefillParams p
       num += w * p.part_o[(slot * BM + r) * HD + d];
     }
   }
-  static_cast<T*>(p.out)[(static_cast<int64_t>(tok) * p.hq + hq) * HD + d] =
-      MmaOp<T>::from_float(den > 0.f ? num / den : 0.f);
+  const int64_t oi = (static_cast<int64_t>(tok) * p.hq + hq) * HD + d;
+  const float val = den > 0.f ? num / den : 0.f;
+  static_cast<T*>(p.out)[oi] =
+      p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[oi]) : MmaOp<T>::from_float(val);
 }
 
 }  // namespace msgl

@@ -28,6 +28,7 @@ struct PrefillParams {
   const int32_t* kv_indices;
   const int32_t* prefix_lens;
   void* out;
+  const void* gate;  // (total_q, hq, D) or null: out *= sigmoid(gate)
   float* part_o;   // (items, hkv, BM, D) unnormalised fp32 partial outputs
   float* part_ml;  // (items, hkv, BM, 2) running max (base-2 units) and sum
   int* plan;       // (batch, 2): first item id and split count of each sequence

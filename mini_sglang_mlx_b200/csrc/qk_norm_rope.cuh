@@ -10,14 +10,16 @@
 // Arithmetic follows the reference's building blocks: RMSNorm y = x * rsqrt(mean(x^2) + eps) * w
 // in fp32, rounded to the 16-bit type (the reference materialises that array); RoPE in the
 // non-interleaved layout (pairs (i, i + rd/2), angle = position * base^(-2i/rd)) in fp32,
-// rounded once more.  head_dim 128, rotary_dim 64 or 128.
+// rounded once more.  head_dim 128 or 256; rotary_dim = head_dim, head_dim/2 or head_dim/4
+// (the reference's Qwen3 layers rotate the whole head, its Qwen3.5 layers a quarter of it).
 //
 // One CTA per token, its warps independent of one another (no shared memory, no CTA
-// barrier).  A half-warp owns a row: lane hl of it holds elements 4hl..4hl+3 and
-// 64+4hl..64+4hl+3 (8-byte accesses, 128 bytes per half-warp), so for rotary_dim 128 both
-// members of a rotary pair sit in the same lane (for rotary_dim 64 the partner is lane ^ 8).
-// A warp has eight rows in flight and the next eight prefetched (the kernel is bound by HBM
-// and needs the bytes in flight), and computes the four rotary angles its lanes need itself.
+// barrier).  A half-warp owns a row: lane hl of it holds E = head_dim/32 consecutive elements
+// of the lower half of the row and the E elements half a row further on (8- or 16-byte
+// accesses), so with rotary_dim == head_dim both members of a rotary pair sit in the same lane
+// (with a smaller rotary_dim the partner is a lane of the same half-warp).  A warp has eight
+// rows in flight (four at head_dim 256) and as many prefetched (the kernel needs the bytes in
+// flight), and computes the rotary angles its lanes need itself.
 #pragma once
 
 #include "common.cuh"
@@ -40,13 +42,6 @@ struct QkNormRopeParams {
   int64_t num_slots;
   float log2_base, eps;
 };
-
-template <typename T>
-__device__ __forceinline__ float to_f32(T x);
-template <>
-__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
-template <>
-__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
 
 // sin and cos of an angle of up to ~2*10^5 rad: the multiple of 2*pi is taken off with a
 // two-constant fused multiply-add (exact to about 3e-7 rad at that size), the rest goes to
@@ -81,11 +76,20 @@ struct Pair16<__half> {
   __device__ __forceinline__ static type pack(float a, float b) { return __floats2half2_rn(a, b); }
 };
 
-template <typename T>
+template <int BYTES>
+struct RowVec;
+template <>
+struct RowVec<8> { using type = uint2; };
+template <>
+struct RowVec<16> { using type = uint4; };
+
+template <typename T, int HD>
 __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRopeParams p) {
-  constexpr int HD = 128;
-  constexpr int RU = 4;  // row pairs a warp has in flight (a half-warp per row)
-  using P2 = typename Pair16<T>::type;
+  static_assert(HD == 128 || HD == 256, "head_dim 128 or 256");
+  constexpr int RU = HD == 128 ? 4 : 2;  // row pairs a warp has in flight (a half-warp per row)
+  constexpr int E = HD / 32;             // elements of a lane in each half of the row
+  constexpr int W = E / 2;               // 32-bit words (16-bit pairs) of those
+  using Vec = typename RowVec<E * 2>::type;
   const int tok = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int hl = lane & 15, side = lane >> 4;   // position inside the half-warp, which row of the pair
@@ -96,49 +100,58 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
     if (row < n_qk) return static_cast<const T*>(p.k) + tok * p.k_stride + (row - p.hq) * HD;
     return static_cast<const T*>(p.v) + tok * p.v_stride + (row - n_qk) * HD;
   };
-  // lane (side, hl) holds elements 4hl..4hl+3 and 64+4hl..64+4hl+3 of row (first + 2u + side)
-  auto load_rows = [&](int first, uint2 (&lo)[RU], uint2 (&hi)[RU]) {
+  // lane (side, hl) holds elements E*hl .. E*hl+E-1 of the lower and of the upper half of
+  // row (first + 2u + side)
+  auto load_rows = [&](int first, Vec (&lo)[RU], Vec (&hi)[RU]) {
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
       const int row = first + 2 * u + side;
       if (row < rows) {
-        const uint2* src = reinterpret_cast<const uint2*>(row_ptr(row));
+        const Vec* src = reinterpret_cast<const Vec*>(row_ptr(row));
         lo[u] = src[hl];
         hi[u] = src[16 + hl];
       }
     }
   };
+  auto word = [](const Vec& v, int i) -> uint32_t { return reinterpret_cast<const uint32_t*>(&v)[i]; };
   // the first rows are on their way while the token's angles are worked out
-  uint2 lo[RU], hi[RU];
+  Vec lo[RU], hi[RU];
   load_rows(warp * 2 * RU, lo, hi);
   const int slot = p.out_loc[tok];
   const bool slot_ok = slot >= 0 && slot < p.num_slots;
-  // this lane's four rotary frequencies: pair index i = 4hl + e of the first half for
-  // rotary_dim 128, 4(hl & 7) + e for rotary_dim 64.  angle = position * base^(-2i/rd): the
-  // product is taken in fp32 as the reference does.
-  const int f0 = half == 64 ? 4 * hl : 4 * (hl & 7);
+  // Rotary pairs are (i, i + half).  With rotary_dim == head_dim the partner of a lane's lower
+  // element is its own upper element.  With a smaller rotary_dim the pairs lie inside the
+  // lower half of the row: lanes below xm hold first members, the partner is lane ^ xm, and
+  // lanes from 2*xm on (and the whole upper half) pass through.  angle = position *
+  // base^(-2i/rd): the product is taken in fp32 as the reference does.
+  const bool in_lane = p.rotary_dim == HD;
+  const int xm = in_lane ? 0 : half / E;
+  const bool rot_lane = in_lane || hl < 2 * xm;
+  const int f0 = in_lane ? E * hl : E * (hl & (xm - 1));
   const float posf = static_cast<float>(p.positions[tok]);
   const float inv_rd = 1.f / static_cast<float>(p.rotary_dim);
-  float cs[4], sn[4];
+  uint64_t cs2[W], sn2[W], ng2[W];
 #pragma unroll
-  for (int e = 0; e < 4; ++e)
-    sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + e)) * inv_rd)), sn[e], cs[e]);
-  // norm weights and rotation factors as packed pairs of floats: elements (0,1) and (2,3) of
-  // the lane's low and high quadruple
-  uint64_t wq[4], wk[4];   // [lo01, lo23, hi01, hi23]
+  for (int w = 0; w < W; ++w) {
+    float c0, s0, c1, s1;
+    sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + 2 * w)) * inv_rd)), s0, c0);
+    sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + 2 * w + 1)) * inv_rd)), s1, c1);
+    cs2[w] = pack_f32x2(c0, c1);
+    sn2[w] = pack_f32x2(s0, s1);
+    ng2[w] = pack_f32x2(-s0, -s1);
+  }
+  // norm weights as packed pairs of floats: [lower words, upper words]
+  uint64_t wq[2 * W], wk[2 * W];
   {
     const T* w = static_cast<const T*>(p.q_weight);
     const T* x = static_cast<const T*>(p.k_weight);
 #pragma unroll
-    for (int h2 = 0; h2 < 4; ++h2) {
-      const int e0 = (h2 >> 1) * 64 + 4 * hl + (h2 & 1) * 2;
-      wq[h2] = w ? pack_f32x2(to_f32(w[e0]), to_f32(w[e0 + 1])) : 0ull;
-      wk[h2] = x ? pack_f32x2(to_f32(x[e0]), to_f32(x[e0 + 1])) : 0ull;
+    for (int i = 0; i < 2 * W; ++i) {
+      const int e0 = (i / W) * (HD / 2) + E * hl + (i % W) * 2;
+      wq[i] = w ? pack_f32x2(to_f32(w[e0]), to_f32(w[e0 + 1])) : 0ull;
+      wk[i] = x ? pack_f32x2(to_f32(x[e0]), to_f32(x[e0 + 1])) : 0ull;
     }
   }
-  const uint64_t cs01 = pack_f32x2(cs[0], cs[1]), cs23 = pack_f32x2(cs[2], cs[3]);
-  const uint64_t sn01 = pack_f32x2(sn[0], sn[1]), sn23 = pack_f32x2(sn[2], sn[3]);
-  const uint64_t ng01 = pack_f32x2(-sn[0], -sn[1]), ng23 = pack_f32x2(-sn[2], -sn[3]);
   auto from_bits2 = [](uint32_t v) -> uint64_t {
     const float2 f = Pair16<T>::from_bits(v);
     return pack_f32x2(f.x, f.y);
@@ -150,7 +163,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
   };
 
   for (int first = warp * 2 * RU; first < rows; first += nwarps * 2 * RU) {
-    uint2 nlo[RU], nhi[RU];   // the next rows, in flight while these are processed
+    Vec nlo[RU], nhi[RU];   // the next rows, in flight while these are processed
     load_rows(first + nwarps * 2 * RU, nlo, nhi);
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
@@ -160,8 +173,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
         // ---- both rows of the pair are V rows (or past the end): copy into the pool
         if (live && slot_ok) {
           T* dst = static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD;
-          reinterpret_cast<uint2*>(dst)[hl] = lo[u];
-          reinterpret_cast<uint2*>(dst)[16 + hl] = hi[u];
+          reinterpret_cast<Vec*>(dst)[hl] = lo[u];
+          reinterpret_cast<Vec*>(dst)[16 + hl] = hi[u];
         }
         continue;
       }
@@ -171,14 +184,21 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
       const bool is_v = live && row >= n_qk;
       const bool is_q = live && row < p.hq;
       const bool has_w = live && !is_v && (is_q ? p.q_weight : p.k_weight) != nullptr;
-      uint64_t a01 = from_bits2(live ? lo[u].x : 0u), a23 = from_bits2(live ? lo[u].y : 0u);
-      uint64_t b01 = from_bits2(live ? hi[u].x : 0u), b23 = from_bits2(live ? hi[u].y : 0u);
+      uint64_t a[W], b[W];
+#pragma unroll
+      for (int w = 0; w < W; ++w) {
+        a[w] = from_bits2(live ? word(lo[u], w) : 0u);
+        b[w] = from_bits2(live ? word(hi[u], w) : 0u);
+      }
       float ss;
       {
-        uint64_t acc = mul_f32x2(a01, a01);
-        acc = fma_f32x2(a23, a23, acc);
-        acc = fma_f32x2(b01, b01, acc);
-        acc = fma_f32x2(b23, b23, acc);
+        uint64_t acc = mul_f32x2(a[0], a[0]);
+        acc = fma_f32x2(b[0], b[0], acc);
+#pragma unroll
+        for (int w = 1; w < W; ++w) {
+          acc = fma_f32x2(a[w], a[w], acc);
+          acc = fma_f32x2(b[w], b[w], acc);
+        }
         float s0, s1;
         unpack_f32x2(acc, s0, s1);
         ss = s0 + s1;
@@ -189,35 +209,34 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
         const float inv = rsqrtf(ss * (1.f / HD) + p.eps);
         const uint64_t inv2 = pack_f32x2(inv, inv);
         // (x * inv) * w, rounded to the 16-bit type as the reference's materialised norm output is
-        a01 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(a01, inv2), is_q ? wq[0] : wk[0])));
-        a23 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(a23, inv2), is_q ? wq[1] : wk[1])));
-        b01 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(b01, inv2), is_q ? wq[2] : wk[2])));
-        b23 = from_bits2(to_bits2(mul_f32x2(mul_f32x2(b23, inv2), is_q ? wq[3] : wk[3])));
+#pragma unroll
+        for (int w = 0; w < W; ++w) {
+          a[w] = from_bits2(to_bits2(mul_f32x2(mul_f32x2(a[w], inv2), is_q ? wq[w] : wk[w])));
+          b[w] = from_bits2(to_bits2(mul_f32x2(mul_f32x2(b[w], inv2), is_q ? wq[W + w] : wk[W + w])));
+        }
       }
-      if (half == 64) {
+      if (in_lane) {
         if (!is_v) {
-          // pairs (4hl+e, 64+4hl+e), both in this lane: a' = a cos - b sin, b' = a sin + b cos
-          const uint64_t x01 = a01, x23 = a23;
-          a01 = fma_f32x2(b01, ng01, mul_f32x2(x01, cs01));
-          a23 = fma_f32x2(b23, ng23, mul_f32x2(x23, cs23));
-          b01 = fma_f32x2(b01, cs01, mul_f32x2(x01, sn01));
-          b23 = fma_f32x2(b23, cs23, mul_f32x2(x23, sn23));
+          // a' = a cos - b sin, b' = a sin + b cos
+#pragma unroll
+          for (int w = 0; w < W; ++w) {
+            const uint64_t x = a[w];
+            a[w] = fma_f32x2(b[w], ng2[w], mul_f32x2(x, cs2[w]));
+            b[w] = fma_f32x2(b[w], cs2[w], mul_f32x2(x, sn2[w]));
+          }
         }
       } else {
-        // rotary_dim 64: pairs (i, i+32) inside the first 64 elements; lanes hl < 8 hold the
-        // first members, hl >= 8 the second (partner lane ^ 8); the upper 64 pass through
-        float a[4], other[4];
-        unpack_f32x2(a01, a[0], a[1]);
-        unpack_f32x2(a23, a[2], a[3]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) other[e] = __shfl_xor_sync(0xffffffffu, a[e], 8);
-        if (!is_v) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            a[e] = hl < 8 ? a[e] * cs[e] - other[e] * sn[e] : other[e] * sn[e] + a[e] * cs[e];
+        for (int w = 0; w < W; ++w) {
+          float x0, x1;
+          unpack_f32x2(a[w], x0, x1);
+          const uint64_t other = pack_f32x2(__shfl_xor_sync(0xffffffffu, x0, xm),
+                                            __shfl_xor_sync(0xffffffffu, x1, xm));
+          if (!is_v && rot_lane) {
+            a[w] = hl < xm ? fma_f32x2(other, ng2[w], mul_f32x2(a[w], cs2[w]))     // first member
+                           : fma_f32x2(other, sn2[w], mul_f32x2(a[w], cs2[w]));    // second member
+          }
         }
-        a01 = pack_f32x2(a[0], a[1]);
-        a23 = pack_f32x2(a[2], a[3]);
       }
       if (!live) continue;
       T* dst;
@@ -228,8 +247,14 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
         dst = is_v ? static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD
                    : static_cast<T*>(p.k_cache) + slot * p.cache_stride + (row - p.hq) * HD;
       }
-      reinterpret_cast<uint2*>(dst)[hl] = is_v ? lo[u] : make_uint2(to_bits2(a01), to_bits2(a23));
-      reinterpret_cast<uint2*>(dst)[16 + hl] = is_v ? hi[u] : make_uint2(to_bits2(b01), to_bits2(b23));
+      Vec olo, ohi;
+#pragma unroll
+      for (int w = 0; w < W; ++w) {
+        reinterpret_cast<uint32_t*>(&olo)[w] = to_bits2(a[w]);
+        reinterpret_cast<uint32_t*>(&ohi)[w] = to_bits2(b[w]);
+      }
+      reinterpret_cast<Vec*>(dst)[hl] = is_v ? lo[u] : olo;
+      reinterpret_cast<Vec*>(dst)[16 + hl] = is_v ? hi[u] : ohi;
     }
 #pragma unroll
     for (int u = 0; u < RU; ++u) {

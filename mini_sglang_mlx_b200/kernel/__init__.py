@@ -87,14 +87,22 @@ def _check_common(op: str, q, k_cache, v_cache, index_arrays, index_msg: str, q_
     _require(k_cache.shape == v_cache.shape, f"{op}: v_cache shape must match k_cache")
 
 
+def _check_gate(op: str, gate, q) -> None:
+    _require(gate.shape == q.shape and gate.dtype == q.dtype and gate.device == q.device
+             and gate.is_contiguous(), f"{op}: gate must match q in shape, dtype and device, contiguous")
+
+
 def paged_decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits,
-                           sm_scale: float, max_kv_splits: int, *, stream=None) -> torch.Tensor:
+                           sm_scale: float, max_kv_splits: int, *, gate=None,
+                           stream=None) -> torch.Tensor:
     """Decode attention of one query token per sequence over its paged KV.
 
     q ``(batch, Hq, D)``; caches ``(num_slots, Hkv, D)``; ``kv_indptr``
     ``(batch+1)``, ``kv_indices`` ``(total_kv)``, ``num_kv_splits`` ``(batch)``
     int32.  Returns ``(batch, Hq, D)`` in q's dtype.  Signature of the
-    reference op: mini-sglang-mlx-kernel/csrc/bindings.cpp:36-44.
+    reference op: mini-sglang-mlx-kernel/csrc/bindings.cpp:36-44.  ``gate`` (not in the
+    reference op; same shape as q) fuses the ``* sigmoid(gate)`` of the reference's Qwen3.5
+    attention layer (models/qwen3_5.py:110) into the final write.
     """
     op = "paged_decode_attention"
     _check_common(op, q, k_cache, v_cache, (kv_indptr, kv_indices, num_kv_splits),
@@ -110,18 +118,22 @@ def paged_decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_sp
     with torch.cuda.device(q.device):
         need = lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits))
         ws = _workspace(need, q.device, sh)
-        _lib.check(lib.msgl_paged_decode_attention(
-            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kv_indptr.data_ptr(),
-            kv_indices.data_ptr(), num_kv_splits.data_ptr(), out.data_ptr(), ws.data_ptr(),
-            ws.numel(), batch, hq, k_cache.shape[1], d, k_cache.shape[0], _DTYPES[q.dtype],
-            float(sm_scale), int(max_kv_splits), sh))
+        tail = (out.data_ptr(), ws.data_ptr(), ws.numel(), batch, hq, k_cache.shape[1], d,
+                k_cache.shape[0], _DTYPES[q.dtype], float(sm_scale), int(max_kv_splits), sh)
+        head = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kv_indptr.data_ptr(),
+                kv_indices.data_ptr(), num_kv_splits.data_ptr())
+        if gate is None:
+            _lib.check(lib.msgl_paged_decode_attention(*head, *tail))
+        else:
+            _check_gate(op, gate, q)
+            _lib.check(lib.msgl_paged_decode_attention_gated(*head, gate.data_ptr(), *tail))
     return out
 
 
 def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens,
                             sm_scale: float, max_len_extend: int, *,
                             is_cross_attention: bool = False, sliding_window_size: int = 0,
-                            stream=None) -> torch.Tensor:
+                            gate=None, stream=None) -> torch.Tensor:
     """Ragged multi-token attention over prefix + extend tokens of paged KV.
 
     q ``(total_q, Hq, D)``; ``qo_indptr``/``kv_indptr`` ``(batch+1)``,
@@ -129,6 +141,7 @@ def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indice
     causal by default; ``is_cross_attention`` drops the causal bound;
     ``sliding_window_size`` W > 0 keeps keys at positions >= pos - W + 1.
     Signature of the reference op: mini-sglang-mlx-kernel/csrc/bindings.cpp:45-55.
+    ``gate`` (not in the reference op; same shape as q): out = attention * sigmoid(gate).
     """
     op = "paged_prefill_attention"
     _check_common(op, q, k_cache, v_cache, (qo_indptr, kv_indptr, kv_indices, prefix_lens),
@@ -148,12 +161,16 @@ def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indice
         need = lib.msgl_prefill_workspace_bytes(batch, total_q, total_kv, hq, k_cache.shape[1], d,
                                                 int(max_len_extend), int(sliding_window_size))
         ws = _workspace(need, q.device, sh)
-        _lib.check(lib.msgl_paged_prefill_attention(
-            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
-            kv_indptr.data_ptr(), kv_indices.data_ptr(), prefix_lens.data_ptr(), out.data_ptr(),
-            ws.data_ptr(), ws.numel(), batch, total_q, total_kv, hq, k_cache.shape[1], d,
-            k_cache.shape[0], _DTYPES[q.dtype], float(sm_scale), int(max_len_extend),
-            int(bool(is_cross_attention)), int(sliding_window_size), sh))
+        head = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
+                kv_indptr.data_ptr(), kv_indices.data_ptr(), prefix_lens.data_ptr())
+        tail = (out.data_ptr(), ws.data_ptr(), ws.numel(), batch, total_q, total_kv, hq, k_cache.shape[1],
+                d, k_cache.shape[0], _DTYPES[q.dtype], float(sm_scale), int(max_len_extend),
+                int(bool(is_cross_attention)), int(sliding_window_size), sh)
+        if gate is None:
+            _lib.check(lib.msgl_paged_prefill_attention(*head, *tail))
+        else:
+            _check_gate(op, gate, q)
+            _lib.check(lib.msgl_paged_prefill_attention_gated(*head, gate.data_ptr(), *tail))
     return out
 
 

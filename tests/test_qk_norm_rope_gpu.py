@@ -14,9 +14,8 @@ from oracle.qk_norm_rope_oracle import qk_norm_rope_store_oracle
 pytestmark = pytest.mark.gpu
 
 
-def _case(n, hq, hkv, dtype, seed, max_pos, num_slots=4096, fused_qkv=False):
+def _case(n, hq, hkv, dtype, seed, max_pos, num_slots=4096, fused_qkv=False, d=128):
     g = torch.Generator().manual_seed(seed)
-    d = 128
     if fused_qkv:
         qkv = torch.randn(n, (hq + 2 * hkv) * d, generator=g).to(dtype)
         q = qkv[:, : hq * d].view(n, hq, d)
@@ -43,11 +42,14 @@ def _check(out, ref, what):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("n,hq,hkv,rd,max_pos", [(1, 16, 8, 128, 10), (37, 32, 8, 128, 40000),
-                                                 (300, 32, 4, 128, 131072), (64, 16, 8, 64, 5000)])
-def test_fused_step_matches_the_separate_ops(dtype, n, hq, hkv, rd, max_pos):
+@pytest.mark.parametrize("n,hq,hkv,d,rd,max_pos", [
+    (1, 16, 8, 128, 128, 10), (37, 32, 8, 128, 128, 40000), (300, 32, 4, 128, 128, 131072),
+    (64, 16, 8, 128, 64, 5000), (33, 7, 3, 128, 32, 900),
+    # head_dim 256: the whole head, half of it, and a quarter (the reference's Qwen3.5 layers)
+    (40, 16, 4, 256, 256, 30000), (9, 8, 2, 256, 128, 70000), (130, 24, 4, 256, 64, 100000), (5, 3, 1, 256, 64, 17)])
+def test_fused_step_matches_the_separate_ops(dtype, n, hq, hkv, d, rd, max_pos):
     from mini_sglang_mlx_b200 import qk_norm_rope_store
-    _, q, k, v, qw, kw, pos, loc, kc, vc = _case(n, hq, hkv, dtype, seed=n + rd, max_pos=max_pos)
+    _, q, k, v, qw, kw, pos, loc, kc, vc = _case(n, hq, hkv, dtype, seed=n + rd, max_pos=max_pos, d=d)
     kc_ref, vc_ref = kc.clone(), vc.clone()
     q_ref = qk_norm_rope_store_oracle(q, k, v, qw, kw, pos, loc, kc_ref, vc_ref,
                                       rope_base=1e6, eps=1e-6, rotary_dim=rd)
@@ -97,9 +99,9 @@ def test_out_of_range_slots_are_dropped_and_bad_arguments_rejected():
     _check(out, q_ref, "q")
     _check(kcd, kc_ref, "k_cache")
     assert torch.equal(vcd.cpu(), vc_ref)
-    with pytest.raises(RuntimeError, match="rotary_dim must be 64 or 128"):
+    with pytest.raises(RuntimeError, match="rotary_dim must be head_dim, head_dim/2 or head_dim/4"):
         qk_norm_rope_store(q.cuda(), k.cuda(), v.cuda(), None, None, pos.cuda(), loc.cuda(), kcd, vcd,
-                           rope_base=1e6, rotary_dim=32)
+                           rope_base=1e6, rotary_dim=48)
     with pytest.raises(RuntimeError, match="positions and out_loc"):
         qk_norm_rope_store(q.cuda(), k.cuda(), v.cuda(), None, None, pos.cuda().long(), loc.cuda(), kcd, vcd,
                            rope_base=1e6)
