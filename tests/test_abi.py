@@ -108,3 +108,24 @@ def test_python_ops_refuse_cpu_tensors():
         paged_decode_attention(q, kc, kc, z, z, z[:1], 0.1, 32)
     with pytest.raises(RuntimeError, match="q must be 3D"):
         paged_decode_attention(q[0], kc, kc, z, z, z[:1], 0.1, 32)
+
+
+def test_prefill_workspace_follows_the_split_policy():
+    """No kernel launch: the scratch size tells whether the key range will be split.  Query tiles
+    that already fill more than half of the CTA slots run unsplit (status area only); verify and
+    draft-block shapes and small chunks over long prefixes get partials for a merge pass."""
+    ws = _lib.lib().msgl_prefill_workspace_bytes
+    status_only = ws(1, 0, 0, 32, 8, 128, 0, 0)
+    # chunked prefill, 4 x 512 query tokens, Hq32/Hkv8: 256 query tiles -> no split
+    assert ws(4, 2048, 12000, 32, 8, 128, 512, 0) == status_only
+    # speculative verify: 32 sequences x 8 tokens over ~300k keys, Hkv 4: 128 tiles of 296 slots -> split
+    verify = ws(32, 256, 303560, 32, 4, 128, 8, 0)
+    assert verify > status_only
+    # one 128-token chunk over a 32k prefix: 16 tiles -> split into many pieces
+    assert ws(1, 128, 32896, 32, 8, 128, 128, 0) > status_only
+    # more keys never need less scratch
+    assert ws(32, 256, 607120, 32, 4, 128, 8, 0) >= verify
+    # head_dim 256 runs one CTA per SM: 128 (sequence, head) units already fill most of 148 slots
+    # (no split), 32 units do not
+    assert ws(32, 256, 303560, 32, 4, 256, 8, 0) == status_only
+    assert ws(8, 64, 75890, 32, 4, 256, 8, 0) > status_only
