@@ -594,6 +594,67 @@ def run_pre_attention_step(args):
         "cpu_baseline": cpu}))
 
 
+def run_store_kv(args):
+    """`--workload store_kv_cache`: the K/V scatter of one prefill chunk into the paged pool
+    (Qwen3-8B shape, Hkv 8, D 128), HBM-bound: rows read once, written once."""
+    from mini_sglang_mlx_b200 import store_kv_cache
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    peaks, peak_kind = load_peaks()
+    n, hkv, d = args.batch or 131072, 8, 128
+    g = torch.Generator().manual_seed(808)
+    k = torch.randn(n, hkv, d, generator=g).bfloat16().to(device)
+    v = torch.randn(n, hkv, d, generator=g).bfloat16().to(device)
+    num_slots = 2 * n
+    loc = torch.randperm(num_slots, generator=g)[:n].int().to(device)
+    kc = torch.zeros(num_slots, hkv, d, dtype=torch.bfloat16, device=device)
+    vc = torch.zeros_like(kc)
+    nbytes = 4 * n * hkv * d * 2 + 4 * n        # k, v read; k, v rows written; slot ids
+    with ClockSampler(device.index) as clocks:
+        for _ in range(args.warmup):
+            store_kv_cache(kc, vc, loc, k, v)
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        for i in range(args.steps):           # 1.07 GB per step: larger than L2
+            starts[i].record()
+            store_kv_cache(kc, vc, loc, k, v)
+            ends[i].record()
+        torch.cuda.synchronize()
+    per = [s_.elapsed_time(e) for s_, e in zip(starts, ends)]
+    ms = sum(per) / len(per)
+    cpu = None
+    if not args.no_cpu:
+        from oracle.paged_attention_oracle import store_kv_cache_oracle
+        cores = use_all_host_threads()
+        m = 16384
+        kc_h = torch.zeros(num_slots, hkv, d, dtype=torch.bfloat16)
+        vc_h = torch.zeros_like(kc_h)
+        k_h, v_h, loc_h = k[:m].cpu(), v[:m].cpu(), loc[:m].cpu()
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < 10.0:
+            store_kv_cache_oracle(kc_h, vc_h, loc_h, k_h, v_h)
+            reps += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": reps * (4 * m * hkv * d * 2 + 4 * m) / dt / 1e9, "unit": "GB/s", "cores": cores,
+               "kind": "port", "sample": f"{m} of {n} tokens per pass, torch-CPU index_copy restatement"}
+    ach = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "K/V scatter into the paged pool, HBM GB/s", "value": ach, "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"store_kv_cache, {n} tokens, Hkv8, D128", "l2": "inputs larger than L2",
+                   "algorithmic_bytes_per_step": nbytes},
+        "clocks": clocks.summary(), "e2e": None, "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": f"{peak_kind} copy bandwidth"},
+        "cpu_baseline": cpu}))
+
+
 def run_reference(args):
     """The CPU path the reference's own tests use as ground truth (gather pages, SDPA), as a
     torch-CPU restatement: MLX is not installable here and the Metal kernels need macOS."""
@@ -657,6 +718,8 @@ def main():
     BATCH_OVERRIDE = args.batch
     if args.workload == "qk_norm_rope_store":
         run_pre_attention_step(args)
+    elif args.workload == "store_kv_cache":
+        run_store_kv(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
