@@ -3,6 +3,7 @@
 // scratch layout, launch configuration.  Declarations: include/msgl_b200.h.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -604,19 +605,24 @@ int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q
   p.log2_base = log2f(rope_base);
   p.eps = eps;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int rows = num_q_heads + 2 * num_kv_heads;
-  const int per_warp = head_dim == 256 ? 8 : 16;   // rows of a warp: two passes of four or eight
-  int threads = 32 * ((rows + per_warp - 1) / per_warp);
-  if (threads > 256) threads = 256;
+  const int threads = 256;                          // sixteen half-warps, an item each per pass
+  int sms = sm_count_cached();
+  if (sms <= 0) sms = 148;
+  const int kR = msgl::qk_rows_per_item(head_dim);
+  const int64_t items = static_cast<int64_t>(n_tokens) *
+                        ((num_q_heads + kR - 1) / kR + 2 * ((num_kv_heads + kR - 1) / kR));
+  if (items >= (1ll << 31)) return fail(MSGL_BAD_ARG, "qk_norm_rope_store: too many rows for one call");
+  const int64_t want = (items + 15) / 16;
+  const int n_ctas = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(sms) * 16));
   if (head_dim == 256) {
     if (dtype == MSGL_DTYPE_BF16)
-      msgl::qk_norm_rope_store_kernel<__nv_bfloat16, 256><<<n_tokens, threads, 0, s>>>(p);
+      msgl::qk_norm_rope_store_kernel<__nv_bfloat16, 256><<<n_ctas, threads, 0, s>>>(p);
     else
-      msgl::qk_norm_rope_store_kernel<__half, 256><<<n_tokens, threads, 0, s>>>(p);
+      msgl::qk_norm_rope_store_kernel<__half, 256><<<n_ctas, threads, 0, s>>>(p);
   } else if (dtype == MSGL_DTYPE_BF16) {
-    msgl::qk_norm_rope_store_kernel<__nv_bfloat16, 128><<<n_tokens, threads, 0, s>>>(p);
+    msgl::qk_norm_rope_store_kernel<__nv_bfloat16, 128><<<n_ctas, threads, 0, s>>>(p);
   } else {
-    msgl::qk_norm_rope_store_kernel<__half, 128><<<n_tokens, threads, 0, s>>>(p);
+    msgl::qk_norm_rope_store_kernel<__half, 128><<<n_ctas, threads, 0, s>>>(p);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("qk_norm_rope_store", e);

@@ -13,13 +13,13 @@
 // rounded once more.  head_dim 128 or 256; rotary_dim = head_dim, head_dim/2 or head_dim/4
 // (the reference's Qwen3 layers rotate the whole head, its Qwen3.5 layers a quarter of it).
 //
-// One CTA per token, its warps independent of one another (no shared memory, no CTA
-// barrier).  A half-warp owns a row: lane hl of it holds E = head_dim/32 consecutive elements
-// of the lower half of the row and the E elements half a row further on (8- or 16-byte
-// accesses), so with rotary_dim == head_dim both members of a rotary pair sit in the same lane
-// (with a smaller rotary_dim the partner is a lane of the same half-warp).  A warp has eight
-// rows in flight (four at head_dim 256) and as many prefetched (the kernel needs the bytes in
-// flight), and computes the rotary angles its lanes need itself.
+// Work items are (token, head) rows, a half-warp each, in a grid-stride loop.  Lane hl of the
+// half-warp holds E = head_dim/32 consecutive elements of the lower half of the row and the
+// E elements half a row further on (8- or 16-byte accesses), so with rotary_dim == head_dim
+// both members of a rotary pair sit in the same lane (with a smaller rotary_dim the partner
+// is a lane of the same half-warp).  The rotary frequencies of a lane are constants; the
+// angles are recomputed per row from the token's position (cheaper than keeping a token's
+// rows together: what this kernel needs is many independent rows in flight).
 #pragma once
 
 #include "common.cuh"
@@ -83,75 +83,36 @@ struct RowVec<8> { using type = uint2; };
 template <>
 struct RowVec<16> { using type = uint4; };
 
+// heads per work item: sixteen bytes of row data in flight per lane and head either way
+__host__ __device__ constexpr int qk_rows_per_item(int head_dim) { return head_dim == 256 ? 2 : 4; }
+
 template <typename T, int HD>
 __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRopeParams p) {
   static_assert(HD == 128 || HD == 256, "head_dim 128 or 256");
-  constexpr int RU = HD == 128 ? 4 : 2;  // row pairs a warp has in flight (a half-warp per row)
   constexpr int E = HD / 32;             // elements of a lane in each half of the row
   constexpr int W = E / 2;               // 32-bit words (16-bit pairs) of those
+  constexpr int R = qk_rows_per_item(HD);
   using Vec = typename RowVec<E * 2>::type;
-  const int tok = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int hl = lane & 15, side = lane >> 4;   // position inside the half-warp, which row of the pair
+  const int lane = threadIdx.x & 31;
+  const int hl = lane & 15;                                   // position inside the half-warp
+  const uint32_t hmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;   // the half-warps run apart
   const int half = p.rotary_dim >> 1;
-  const int n_qk = p.hq + p.hkv, rows = n_qk + p.hkv;
-  auto row_ptr = [&](int row) -> const T* {
-    if (row < p.hq) return static_cast<const T*>(p.q) + tok * p.q_stride + row * HD;
-    if (row < n_qk) return static_cast<const T*>(p.k) + tok * p.k_stride + (row - p.hq) * HD;
-    return static_cast<const T*>(p.v) + tok * p.v_stride + (row - n_qk) * HD;
-  };
-  // lane (side, hl) holds elements E*hl .. E*hl+E-1 of the lower and of the upper half of
-  // row (first + 2u + side)
-  auto load_rows = [&](int first, Vec (&lo)[RU], Vec (&hi)[RU]) {
-#pragma unroll
-    for (int u = 0; u < RU; ++u) {
-      const int row = first + 2 * u + side;
-      if (row < rows) {
-        const Vec* src = reinterpret_cast<const Vec*>(row_ptr(row));
-        lo[u] = src[hl];
-        hi[u] = src[16 + hl];
-      }
-    }
-  };
-  auto word = [](const Vec& v, int i) -> uint32_t { return reinterpret_cast<const uint32_t*>(&v)[i]; };
-  // the first rows are on their way while the token's angles are worked out
-  Vec lo[RU], hi[RU];
-  load_rows(warp * 2 * RU, lo, hi);
-  const int slot = p.out_loc[tok];
-  const bool slot_ok = slot >= 0 && slot < p.num_slots;
   // Rotary pairs are (i, i + half).  With rotary_dim == head_dim the partner of a lane's lower
   // element is its own upper element.  With a smaller rotary_dim the pairs lie inside the
   // lower half of the row: lanes below xm hold first members, the partner is lane ^ xm, and
-  // lanes from 2*xm on (and the whole upper half) pass through.  angle = position *
-  // base^(-2i/rd): the product is taken in fp32 as the reference does.
+  // lanes from 2*xm on (and the whole upper half) pass through.
   const bool in_lane = p.rotary_dim == HD;
   const int xm = in_lane ? 0 : half / E;
   const bool rot_lane = in_lane || hl < 2 * xm;
   const int f0 = in_lane ? E * hl : E * (hl & (xm - 1));
-  const float posf = static_cast<float>(p.positions[tok]);
-  const float inv_rd = 1.f / static_cast<float>(p.rotary_dim);
-  uint64_t cs2[W], sn2[W], ng2[W];
-#pragma unroll
-  for (int w = 0; w < W; ++w) {
-    float c0, s0, c1, s1;
-    sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + 2 * w)) * inv_rd)), s0, c0);
-    sincos_reduced(posf * exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + 2 * w + 1)) * inv_rd)), s1, c1);
-    cs2[w] = pack_f32x2(c0, c1);
-    sn2[w] = pack_f32x2(s0, s1);
-    ng2[w] = pack_f32x2(-s0, -s1);
-  }
-  // norm weights as packed pairs of floats: [lower words, upper words]
-  uint64_t wq[2 * W], wk[2 * W];
+  // this lane's rotary frequencies base^(-2i/rd): the same for every token
+  float freq[E];
   {
-    const T* w = static_cast<const T*>(p.q_weight);
-    const T* x = static_cast<const T*>(p.k_weight);
+    const float inv_rd = 1.f / static_cast<float>(p.rotary_dim);
 #pragma unroll
-    for (int i = 0; i < 2 * W; ++i) {
-      const int e0 = (i / W) * (HD / 2) + E * hl + (i % W) * 2;
-      wq[i] = w ? pack_f32x2(to_f32(w[e0]), to_f32(w[e0 + 1])) : 0ull;
-      wk[i] = x ? pack_f32x2(to_f32(x[e0]), to_f32(x[e0 + 1])) : 0ull;
-    }
+    for (int e = 0; e < E; ++e) freq[e] = exp2f(-p.log2_base * (static_cast<float>(2 * (f0 + e)) * inv_rd));
   }
+  auto word = [](const Vec& v, int i) -> uint32_t { return reinterpret_cast<const uint32_t*>(&v)[i]; };
   auto from_bits2 = [](uint32_t v) -> uint64_t {
     const float2 f = Pair16<T>::from_bits(v);
     return pack_f32x2(f.x, f.y);
@@ -162,36 +123,86 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
     return MmaOp<T>::pack(x, y);
   };
 
-  for (int first = warp * 2 * RU; first < rows; first += nwarps * 2 * RU) {
-    Vec nlo[RU], nhi[RU];   // the next rows, in flight while these are processed
-    load_rows(first + nwarps * 2 * RU, nlo, nhi);
+  // A work item is up to R consecutive heads of one token and one kind (q, k or v), handled by
+  // a half-warp; items are taken in a grid-stride loop.  The kernel has to retire a row every
+  // ~24 cycles per SM to keep up with HBM, i.e. it is bound by instruction issue as much as by
+  // latency: the angles, the norm weights and the index arithmetic are per item, not per row,
+  // and V items are plain copies.
+  const uint32_t gq = (p.hq + R - 1) / R, gk = (p.hkv + R - 1) / R;
+  const uint32_t groups = gq + 2 * gk;
+  const uint32_t total = static_cast<uint32_t>(p.n) * groups;
+  const uint32_t stride = gridDim.x * (blockDim.x >> 4);
+  for (uint32_t item = (blockIdx.x * blockDim.x + threadIdx.x) >> 4; item < total; item += stride) {
+    const uint32_t tok = item / groups;
+    const uint32_t g = item - tok * groups;
+    const bool is_q = g < gq, is_v = g >= gq + gk;
+    const int h0 = static_cast<int>(is_q ? g : is_v ? g - gq - gk : g - gq) * R;   // first head
+    const int cnt = min(R, (is_q ? p.hq : p.hkv) - h0);
+    const T* src = is_q   ? static_cast<const T*>(p.q) + tok * p.q_stride
+                   : is_v ? static_cast<const T*>(p.v) + tok * p.v_stride
+                          : static_cast<const T*>(p.k) + tok * p.k_stride;
+    src += h0 * HD;
+    Vec lo[R], hi[R];
 #pragma unroll
-    for (int u = 0; u < RU; ++u) {
-      const int row = first + 2 * u + side;
-      const bool live = row < rows;
-      if (first + 2 * u >= n_qk) {
-        // ---- both rows of the pair are V rows (or past the end): copy into the pool
-        if (live && slot_ok) {
-          T* dst = static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD;
-          reinterpret_cast<Vec*>(dst)[hl] = lo[u];
-          reinterpret_cast<Vec*>(dst)[16 + hl] = hi[u];
-        }
-        continue;
+    for (int r = 0; r < R; ++r) {
+      if (r < cnt) {
+        lo[r] = reinterpret_cast<const Vec*>(src + r * HD)[hl];
+        hi[r] = reinterpret_cast<const Vec*>(src + r * HD)[16 + hl];
       }
-      // the two half-warps may still hold rows of different kinds (last q row / first k row,
-      // last k row / first v row): every decision below is per half-warp, the shuffles stay
-      // inside it
-      const bool is_v = live && row >= n_qk;
-      const bool is_q = live && row < p.hq;
-      const bool has_w = live && !is_v && (is_q ? p.q_weight : p.k_weight) != nullptr;
+    }
+    T* dst;
+    if (is_q) {
+      dst = static_cast<T*>(p.q) + tok * p.q_stride + h0 * HD;
+    } else {
+      const int slot = p.out_loc[tok];
+      if (slot < 0 || slot >= p.num_slots) continue;
+      dst = static_cast<T*>(is_v ? p.v_cache : p.k_cache) + slot * p.cache_stride + h0 * HD;
+    }
+    if (is_v) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (r < cnt) {
+          reinterpret_cast<Vec*>(dst + r * HD)[hl] = lo[r];
+          reinterpret_cast<Vec*>(dst + r * HD)[16 + hl] = hi[r];
+        }
+      }
+      continue;
+    }
+    // angle = position * freq: the product is taken in fp32 as the reference does
+    const float posf = static_cast<float>(p.positions[tok]);
+    // a' = a cos + other * sa, where other is the pair's second member with sa = -sin for a
+    // first member, and the first member with sa = +sin for a second member held by another
+    // lane; with both members in this lane b' = b cos + a * sb, sb = +sin.
+    uint64_t cs2[W], sa2[W], sb2[W];
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      float c0, s0, c1, s1;
+      sincos_reduced(posf * freq[2 * w], s0, c0);
+      sincos_reduced(posf * freq[2 * w + 1], s1, c1);
+      cs2[w] = pack_f32x2(c0, c1);
+      sb2[w] = pack_f32x2(s0, s1);
+      sa2[w] = (!in_lane && hl >= xm) ? sb2[w] : pack_f32x2(-s0, -s1);
+    }
+    const T* wt = static_cast<const T*>(is_q ? p.q_weight : p.k_weight);
+    uint64_t wl[W], wh[W];
+    if (wt != nullptr) {
+      const Vec l = reinterpret_cast<const Vec*>(wt)[hl], h = reinterpret_cast<const Vec*>(wt)[16 + hl];
+#pragma unroll
+      for (int w = 0; w < W; ++w) {
+        wl[w] = from_bits2(word(l, w));
+        wh[w] = from_bits2(word(h, w));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (r >= cnt) break;
       uint64_t a[W], b[W];
 #pragma unroll
       for (int w = 0; w < W; ++w) {
-        a[w] = from_bits2(live ? word(lo[u], w) : 0u);
-        b[w] = from_bits2(live ? word(hi[u], w) : 0u);
+        a[w] = from_bits2(word(lo[r], w));
+        b[w] = from_bits2(word(hi[r], w));
       }
-      float ss;
-      {
+      if (wt != nullptr) {
         uint64_t acc = mul_f32x2(a[0], a[0]);
         acc = fma_f32x2(b[0], b[0], acc);
 #pragma unroll
@@ -201,51 +212,33 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
         }
         float s0, s1;
         unpack_f32x2(acc, s0, s1);
-        ss = s0 + s1;
-      }
+        float ss = s0 + s1;
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (has_w) {
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(hmask, ss, o);
         const float inv = rsqrtf(ss * (1.f / HD) + p.eps);
         const uint64_t inv2 = pack_f32x2(inv, inv);
         // (x * inv) * w, rounded to the 16-bit type as the reference's materialised norm output is
 #pragma unroll
         for (int w = 0; w < W; ++w) {
-          a[w] = from_bits2(to_bits2(mul_f32x2(mul_f32x2(a[w], inv2), is_q ? wq[w] : wk[w])));
-          b[w] = from_bits2(to_bits2(mul_f32x2(mul_f32x2(b[w], inv2), is_q ? wq[W + w] : wk[W + w])));
+          a[w] = from_bits2(to_bits2(mul_f32x2(mul_f32x2(a[w], inv2), wl[w])));
+          b[w] = from_bits2(to_bits2(mul_f32x2(mul_f32x2(b[w], inv2), wh[w])));
         }
       }
       if (in_lane) {
-        if (!is_v) {
-          // a' = a cos - b sin, b' = a sin + b cos
 #pragma unroll
-          for (int w = 0; w < W; ++w) {
-            const uint64_t x = a[w];
-            a[w] = fma_f32x2(b[w], ng2[w], mul_f32x2(x, cs2[w]));
-            b[w] = fma_f32x2(b[w], cs2[w], mul_f32x2(x, sn2[w]));
-          }
+        for (int w = 0; w < W; ++w) {
+          const uint64_t x = a[w];
+          a[w] = fma_f32x2(b[w], sa2[w], mul_f32x2(x, cs2[w]));
+          b[w] = fma_f32x2(x, sb2[w], mul_f32x2(b[w], cs2[w]));
         }
       } else {
 #pragma unroll
         for (int w = 0; w < W; ++w) {
           float x0, x1;
           unpack_f32x2(a[w], x0, x1);
-          const uint64_t other = pack_f32x2(__shfl_xor_sync(0xffffffffu, x0, xm),
-                                            __shfl_xor_sync(0xffffffffu, x1, xm));
-          if (!is_v && rot_lane) {
-            a[w] = hl < xm ? fma_f32x2(other, ng2[w], mul_f32x2(a[w], cs2[w]))     // first member
-                           : fma_f32x2(other, sn2[w], mul_f32x2(a[w], cs2[w]));    // second member
-          }
+          const uint64_t other = pack_f32x2(__shfl_xor_sync(hmask, x0, xm), __shfl_xor_sync(hmask, x1, xm));
+          if (rot_lane) a[w] = fma_f32x2(other, sa2[w], mul_f32x2(a[w], cs2[w]));
         }
-      }
-      if (!live) continue;
-      T* dst;
-      if (is_q) {
-        dst = static_cast<T*>(p.q) + tok * p.q_stride + row * HD;
-      } else {
-        if (!slot_ok) continue;
-        dst = is_v ? static_cast<T*>(p.v_cache) + slot * p.cache_stride + (row - n_qk) * HD
-                   : static_cast<T*>(p.k_cache) + slot * p.cache_stride + (row - p.hq) * HD;
       }
       Vec olo, ohi;
 #pragma unroll
@@ -253,13 +246,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkNormRop
         reinterpret_cast<uint32_t*>(&olo)[w] = to_bits2(a[w]);
         reinterpret_cast<uint32_t*>(&ohi)[w] = to_bits2(b[w]);
       }
-      reinterpret_cast<Vec*>(dst)[hl] = is_v ? lo[u] : olo;
-      reinterpret_cast<Vec*>(dst)[16 + hl] = is_v ? hi[u] : ohi;
-    }
-#pragma unroll
-    for (int u = 0; u < RU; ++u) {
-      lo[u] = nlo[u];
-      hi[u] = nhi[u];
+      reinterpret_cast<Vec*>(dst + r * HD)[hl] = olo;
+      reinterpret_cast<Vec*>(dst + r * HD)[16 + hl] = ohi;
     }
   }
 }
