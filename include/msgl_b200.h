@@ -199,6 +199,48 @@ int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
                            int32_t* kv_indices, int batch, int64_t total_kv, void* stream);
 
 /*
+ * Page-granular index entries.  The reference hard-wires one token per page
+ * (mini_sglang_mlx/engine/engine.py:103) and hands the ops one slot id per token
+ * (kv_indices, mini_sglang_mlx/attention/backend.py:239-244, 279-284).  A pool
+ * allocated in pages of page_size tokens (slot = page * page_size + offset) is
+ * described more compactly by one id per PAGE: page_indptr (batch+1),
+ * page_indices (total_pages) and the token lengths kv_lens (batch), all int32
+ * device arrays.  These entries take that form; they build kv_indptr and the
+ * per-token slot ids on the device (a scan of the lengths and one 4-byte store
+ * per token, in front of the same kernels) and then run the op above.
+ * A length that is negative or exceeds page_size * (pages of the sequence)
+ * sets the device status word to 2 and is clamped.
+ *
+ * Workspace: the op's own scratch followed by the index scratch,
+ *   decode : round_up(msgl_decode_workspace_bytes(...), 256)
+ *            + msgl_page_index_workspace_bytes(batch, total_pages, page_size)
+ *   prefill: msgl_prefill_workspace_bytes_p16(...)
+ * total_pages * page_size must be below 2^31.
+ */
+size_t msgl_page_index_workspace_bytes(int batch, int64_t total_pages, int page_size);
+
+int msgl_paged_decode_attention_p16(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* page_indptr, const int32_t* page_indices, const int32_t* kv_lens,
+    const int32_t* num_kv_splits, void* out, void* workspace, size_t workspace_bytes,
+    int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t num_slots,
+    int dtype, float sm_scale, int max_kv_splits, int page_size, int64_t total_pages,
+    void* stream);
+
+size_t msgl_prefill_workspace_bytes_p16(int batch, int total_q, int64_t total_pages, int page_size,
+                                        int num_q_heads, int num_kv_heads, int head_dim,
+                                        int max_len_extend, int sliding_window_size);
+
+int msgl_paged_prefill_attention_p16(
+    const void* q, const void* k_cache, const void* v_cache,
+    const int32_t* qo_indptr, const int32_t* page_indptr, const int32_t* page_indices,
+    const int32_t* kv_lens, const int32_t* prefix_lens, void* out, void* workspace,
+    size_t workspace_bytes, int batch, int total_q, int num_q_heads, int num_kv_heads,
+    int head_dim, int64_t num_slots, int dtype, float sm_scale, int max_len_extend,
+    int is_cross_attention, int sliding_window_size, int page_size, int64_t total_pages,
+    void* stream);
+
+/*
  * Length of the common prefix of two token-id keys in HOST memory (the first
  * index at which they differ), elem_bytes 4 (int32) or 8 (int64); -1 for any
  * other element size.  Used by the radix prefix cache when it walks an edge.

@@ -10,13 +10,17 @@ from .kernel import (  # noqa: F401
     qk_norm_rope_store,
     gather_kv_indices,
     paged_decode_attention,
+    paged_decode_attention_p16,
     paged_prefill_attention,
+    paged_prefill_attention_p16,
     store_kv_cache,
 )
 
 __all__ = [
     "paged_decode_attention",
     "paged_prefill_attention",
+    "paged_decode_attention_p16",
+    "paged_prefill_attention_p16",
     "store_kv_cache",
     "gather_kv_indices",
     "fast_compare_key",

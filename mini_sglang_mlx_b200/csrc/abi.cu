@@ -202,6 +202,62 @@ __global__ void gather_kv_indices_kernel(const int32_t* __restrict__ page_table,
     kv_indices[begin + t] = row[t];
 }
 
+// Page-granular index entries: kv_indptr = exclusive scan of the sequence lengths (one CTA),
+// then one slot id per token, slot = page * page_size + offset inside the page.  A length that
+// is negative or longer than the sequence's pages is reported in the status word and clamped.
+__global__ void __launch_bounds__(1024) page_lens_scan_kernel(const int32_t* __restrict__ kv_lens,
+                                                              const int32_t* __restrict__ page_indptr,
+                                                              int batch, int page_size,
+                                                              int32_t* __restrict__ kv_indptr,
+                                                              int* status) {
+  __shared__ int s_sum[1024];
+  __shared__ int s_carry;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    s_carry = 0;
+    kv_indptr[0] = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < batch; base += 1024) {
+    const int i = base + tid;
+    int len = 0;
+    if (i < batch) {
+      len = kv_lens[i];
+      const int64_t cap = static_cast<int64_t>(page_indptr[i + 1] - page_indptr[i]) * page_size;
+      if (len < 0 || len > cap) {
+        if (status) atomicExch(status, 2);
+        len = len < 0 ? 0 : static_cast<int>(cap < 0 ? 0 : cap);
+      }
+    }
+    s_sum[tid] = len;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+      const int v = tid >= off ? s_sum[tid - off] : 0;
+      __syncthreads();
+      s_sum[tid] += v;
+      __syncthreads();
+    }
+    if (i < batch) kv_indptr[i + 1] = s_carry + s_sum[tid];
+    __syncthreads();
+    if (tid == 1023) s_carry += s_sum[1023];
+    __syncthreads();
+  }
+}
+
+__global__ void expand_page_indices_kernel(const int32_t* __restrict__ page_indptr,
+                                           const int32_t* __restrict__ page_indices,
+                                           const int32_t* __restrict__ kv_indptr, int page_size,
+                                           int32_t* __restrict__ kv_indices) {
+  const int b = blockIdx.y;
+  const int begin = kv_indptr[b];
+  const int len = kv_indptr[b + 1] - begin;
+  const int32_t* pages = page_indices + page_indptr[b];
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < len; t += gridDim.x * blockDim.x) {
+    const int pg = t / page_size;
+    kv_indices[begin + t] = pages[pg] * page_size + (t - pg * page_size);
+  }
+}
+
 template <typename T>
 int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s) {
   dim3 grid1(p.max_splits, p.hkv, p.batch);
@@ -627,6 +683,118 @@ int msgl_qk_norm_rope_store(void* q, const void* k, const void* v, const void* q
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("qk_norm_rope_store", e);
   return MSGL_OK;
+}
+
+size_t msgl_page_index_workspace_bytes(int batch, int64_t total_pages, int page_size) {
+  if (batch <= 0 || total_pages <= 0 || page_size <= 0) return 256;
+  const size_t n = static_cast<size_t>(batch) + 1 + static_cast<size_t>(total_pages) * page_size;
+  return (n * sizeof(int32_t) + 255) / 256 * 256;
+}
+
+// Builds kv_indptr and per-token kv_indices in `index_ws`; *total_kv_bound = total_pages * page_size.
+static int expand_page_index(const char* op_name, const int32_t* page_indptr,
+                             const int32_t* page_indices, const int32_t* kv_lens, int batch,
+                             int64_t total_pages, int page_size, void* index_ws, int* status,
+                             const int32_t** kv_indptr, const int32_t** kv_indices,
+                             int64_t* total_kv_bound, void* stream) {
+  const std::string op = std::string(op_name) + ": ";
+  if (batch < 0 || total_pages < 0) return fail(MSGL_BAD_SHAPE, op + "negative size");
+  if (page_size <= 0) return fail(MSGL_BAD_ARG, op + "page_size must be > 0");
+  if (batch > 65535) return fail(MSGL_BAD_SHAPE, op + "batch must be <= 65535");
+  if (total_pages * page_size >= (1ll << 31))
+    return fail(MSGL_BAD_SHAPE, op + "total_pages * page_size must be < 2^31");
+  if (batch > 0 && (!page_indptr || !kv_lens || (total_pages > 0 && !page_indices)))
+    return fail(MSGL_BAD_ARG, op + "null tensor pointer");
+  int32_t* indptr = static_cast<int32_t*>(index_ws);
+  int32_t* indices = indptr + batch + 1;
+  *kv_indptr = indptr;
+  *kv_indices = indices;
+  *total_kv_bound = total_pages * page_size;
+  if (batch == 0) return MSGL_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  page_lens_scan_kernel<<<1, 1024, 0, s>>>(kv_lens, page_indptr, batch, page_size, indptr, status);
+  if (total_pages > 0) {
+    const int64_t avg = *total_kv_bound / batch + 1;
+    int bx = static_cast<int>((avg + 255) / 256);
+    if (bx > 64) bx = 64;
+    expand_page_indices_kernel<<<dim3(bx, batch), 256, 0, s>>>(page_indptr, page_indices, indptr,
+                                                                page_size, indices);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(op_name, e);
+  return MSGL_OK;
+}
+
+int msgl_paged_decode_attention_p16(const void* q, const void* k_cache, const void* v_cache,
+                                    const int32_t* page_indptr, const int32_t* page_indices,
+                                    const int32_t* kv_lens, const int32_t* num_kv_splits, void* out,
+                                    void* workspace, size_t workspace_bytes, int batch,
+                                    int num_q_heads, int num_kv_heads, int head_dim,
+                                    int64_t num_slots, int dtype, float sm_scale, int max_kv_splits,
+                                    int page_size, int64_t total_pages, void* stream) {
+  const char* op = "paged_decode_attention_p16";
+  if (batch < 0 || num_q_heads <= 0 || head_dim <= 0 || max_kv_splits <= 0 || total_pages < 0 ||
+      page_size <= 0)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + ": bad sizes");
+  const size_t op_ws = (msgl_decode_workspace_bytes(batch, num_q_heads, head_dim, max_kv_splits) + 255) / 256 * 256;
+  const size_t idx_ws = msgl_page_index_workspace_bytes(batch, total_pages, page_size);
+  if (!workspace || workspace_bytes < op_ws + idx_ws)
+    return fail(MSGL_BAD_ARG, std::string(op) + ": workspace too small: need " +
+                                  std::to_string(op_ws + idx_ws) + " bytes, got " +
+                                  std::to_string(workspace_bytes));
+  const int32_t *kv_indptr = nullptr, *kv_indices = nullptr;
+  int64_t bound = 0;
+  int rc = expand_page_index(op, page_indptr, page_indices, kv_lens, batch, total_pages, page_size,
+                             static_cast<unsigned char*>(workspace) + op_ws,
+                             static_cast<int*>(workspace), &kv_indptr, &kv_indices, &bound, stream);
+  if (rc != MSGL_OK) return rc;
+  return decode_impl(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, nullptr, out, workspace,
+                     op_ws, batch, num_q_heads, num_kv_heads, head_dim, num_slots, dtype, sm_scale,
+                     max_kv_splits, stream);
+}
+
+size_t msgl_prefill_workspace_bytes_p16(int batch, int total_q, int64_t total_pages, int page_size,
+                                        int num_q_heads, int num_kv_heads, int head_dim,
+                                        int max_len_extend, int sliding_window_size) {
+  if (total_pages < 0 || page_size <= 0) return 0;
+  const size_t op_ws = (msgl_prefill_workspace_bytes(batch, total_q, total_pages * page_size, num_q_heads,
+                                                     num_kv_heads, head_dim, max_len_extend,
+                                                     sliding_window_size) + 255) / 256 * 256;
+  return op_ws + msgl_page_index_workspace_bytes(batch, total_pages, page_size);
+}
+
+int msgl_paged_prefill_attention_p16(const void* q, const void* k_cache, const void* v_cache,
+                                     const int32_t* qo_indptr, const int32_t* page_indptr,
+                                     const int32_t* page_indices, const int32_t* kv_lens,
+                                     const int32_t* prefix_lens, void* out, void* workspace,
+                                     size_t workspace_bytes, int batch, int total_q, int num_q_heads,
+                                     int num_kv_heads, int head_dim, int64_t num_slots, int dtype,
+                                     float sm_scale, int max_len_extend, int is_cross_attention,
+                                     int sliding_window_size, int page_size, int64_t total_pages,
+                                     void* stream) {
+  const char* op = "paged_prefill_attention_p16";
+  if (batch < 0 || total_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || total_pages < 0 ||
+      page_size <= 0)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + ": bad sizes");
+  const size_t idx_ws = msgl_page_index_workspace_bytes(batch, total_pages, page_size);
+  const size_t total = msgl_prefill_workspace_bytes_p16(batch, total_q, total_pages, page_size,
+                                                        num_q_heads, num_kv_heads, head_dim,
+                                                        max_len_extend, sliding_window_size);
+  if (!workspace || workspace_bytes < total)
+    return fail(MSGL_BAD_ARG, std::string(op) + ": workspace too small: need " +
+                                  std::to_string(total) + " bytes, got " +
+                                  std::to_string(workspace_bytes));
+  const size_t op_ws = total - idx_ws;
+  const int32_t *kv_indptr = nullptr, *kv_indices = nullptr;
+  int64_t bound = 0;
+  int rc = expand_page_index(op, page_indptr, page_indices, kv_lens, batch, total_pages, page_size,
+                             static_cast<unsigned char*>(workspace) + op_ws,
+                             static_cast<int*>(workspace), &kv_indptr, &kv_indices, &bound, stream);
+  if (rc != MSGL_OK) return rc;
+  return prefill_impl(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens, nullptr, out,
+                      workspace, op_ws, batch, total_q, bound, num_q_heads, num_kv_heads, head_dim,
+                      num_slots, dtype, sm_scale, max_len_extend, is_cross_attention,
+                      sliding_window_size, stream);
 }
 
 int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64_t len_b,

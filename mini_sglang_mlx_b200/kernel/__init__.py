@@ -19,6 +19,8 @@ from .. import _lib
 __all__ = [
     "paged_decode_attention",
     "paged_prefill_attention",
+    "paged_decode_attention_p16",
+    "paged_prefill_attention_p16",
     "store_kv_cache",
     "gather_kv_indices",
     "fast_compare_key",
@@ -171,6 +173,77 @@ def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indice
         else:
             _check_gate(op, gate, q)
             _lib.check(lib.msgl_paged_prefill_attention_gated(*head, gate.data_ptr(), *tail))
+    return out
+
+
+def paged_decode_attention_p16(q, k_cache, v_cache, page_indptr, page_indices, kv_lens, num_kv_splits,
+                               sm_scale: float, max_kv_splits: int, *, page_size: int = 16,
+                               stream=None) -> torch.Tensor:
+    """``paged_decode_attention`` for a pool allocated in pages of ``page_size`` tokens
+    (slot = page * page_size + offset): ``page_indptr`` ``(batch+1)``, ``page_indices``
+    ``(total_pages)`` and the token lengths ``kv_lens`` ``(batch)`` replace the per-token
+    ``kv_indptr`` / ``kv_indices`` of the reference op (the reference hard-wires one token per
+    page, mini_sglang_mlx/engine/engine.py:103).  No host synchronisation: the per-token ids
+    are built on the device in front of the same kernels."""
+    op = "paged_decode_attention_p16"
+    _check_common(op, q, k_cache, v_cache, (page_indptr, page_indices, kv_lens, num_kv_splits),
+                  "page_indptr, page_indices, kv_lens, num_kv_splits must be 1D",
+                  "q must be 3D (batch, num_q_heads, head_dim)")
+    batch, hq, d = q.shape
+    _require(k_cache.shape[2] == d, f"{op}: cache head_dim must match q head_dim")
+    _require(page_indptr.numel() == batch + 1 and kv_lens.numel() == batch
+             and num_kv_splits.numel() == batch,
+             f"{op}: page_indptr must have batch+1, kv_lens and num_kv_splits batch entries")
+    _require(int(page_size) > 0, f"{op}: page_size must be > 0")
+    out = torch.empty_like(q)
+    sh = _stream_handle(stream, q.device)
+    lib = _lib.lib()
+    total_pages = page_indices.numel()
+    with torch.cuda.device(q.device):
+        need = ((lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits)) + 255) // 256 * 256
+                + lib.msgl_page_index_workspace_bytes(batch, total_pages, int(page_size)))
+        ws = _workspace(need, q.device, sh)
+        _lib.check(lib.msgl_paged_decode_attention_p16(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_indptr.data_ptr(),
+            page_indices.data_ptr(), kv_lens.data_ptr(), num_kv_splits.data_ptr(), out.data_ptr(),
+            ws.data_ptr(), ws.numel(), batch, hq, k_cache.shape[1], d, k_cache.shape[0],
+            _DTYPES[q.dtype], float(sm_scale), int(max_kv_splits), int(page_size), total_pages, sh))
+    return out
+
+
+def paged_prefill_attention_p16(q, k_cache, v_cache, qo_indptr, page_indptr, page_indices, kv_lens,
+                                prefix_lens, sm_scale: float, max_len_extend: int, *,
+                                page_size: int = 16, is_cross_attention: bool = False,
+                                sliding_window_size: int = 0, stream=None) -> torch.Tensor:
+    """``paged_prefill_attention`` with one id per page of ``page_size`` tokens instead of one
+    per token; see ``paged_decode_attention_p16``."""
+    op = "paged_prefill_attention_p16"
+    _check_common(op, q, k_cache, v_cache, (qo_indptr, page_indptr, page_indices, kv_lens, prefix_lens),
+                  "qo_indptr, page_indptr, page_indices, kv_lens, prefix_lens must be 1D",
+                  "q must be 3D (total_q_tokens, num_q_heads, head_dim)")
+    total_q, hq, d = q.shape
+    _require(k_cache.shape[2] == d, f"{op}: cache head_dim must match q head_dim")
+    batch = qo_indptr.numel() - 1
+    _require(batch > 0, f"{op}: batch must be > 0")
+    _require(page_indptr.numel() == batch + 1 and kv_lens.numel() == batch
+             and prefix_lens.numel() == batch,
+             f"{op}: page_indptr must have batch+1, kv_lens and prefix_lens batch entries")
+    _require(int(page_size) > 0, f"{op}: page_size must be > 0")
+    out = torch.empty_like(q)
+    sh = _stream_handle(stream, q.device)
+    lib = _lib.lib()
+    total_pages = page_indices.numel()
+    with torch.cuda.device(q.device):
+        need = lib.msgl_prefill_workspace_bytes_p16(batch, total_q, total_pages, int(page_size), hq,
+                                                    k_cache.shape[1], d, int(max_len_extend),
+                                                    int(sliding_window_size))
+        ws = _workspace(need, q.device, sh)
+        _lib.check(lib.msgl_paged_prefill_attention_p16(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
+            page_indptr.data_ptr(), page_indices.data_ptr(), kv_lens.data_ptr(), prefix_lens.data_ptr(),
+            out.data_ptr(), ws.data_ptr(), ws.numel(), batch, total_q, hq, k_cache.shape[1], d,
+            k_cache.shape[0], _DTYPES[q.dtype], float(sm_scale), int(max_len_extend),
+            int(bool(is_cross_attention)), int(sliding_window_size), int(page_size), total_pages, sh))
     return out
 
 

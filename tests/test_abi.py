@@ -129,3 +129,13 @@ def test_prefill_workspace_follows_the_split_policy():
     # (no split), 32 units do not
     assert ws(32, 256, 303560, 32, 4, 256, 8, 0) == status_only
     assert ws(8, 64, 75890, 32, 4, 256, 8, 0) > status_only
+
+
+def test_page_granular_workspace_queries_are_host_arithmetic():
+    lib = _lib.lib()
+    idx = lib.msgl_page_index_workspace_bytes(4, 1000, 16)
+    assert idx == ((4 + 1 + 16000) * 4 + 255) // 256 * 256
+    assert lib.msgl_page_index_workspace_bytes(0, 0, 16) == 256
+    op = lib.msgl_prefill_workspace_bytes(4, 2048, 16000, 32, 8, 128, 512, 0)
+    both = lib.msgl_prefill_workspace_bytes_p16(4, 2048, 1000, 16, 32, 8, 128, 512, 0)
+    assert both == (op + 255) // 256 * 256 + idx
