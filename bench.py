@@ -184,18 +184,39 @@ def max_over_ranks(x: float, dist_on: bool) -> float:
     return float(t.item())
 
 
+GRAPH_REPLAY = False  # --graph: the operator call captured once in a CUDA graph, steps replay it
+
+
 def time_kernel_steps(w, steps: int, warmup: int, dist_on: bool, flush):
     """Sum of per-step device times (ms) of `steps` operator calls, L2 flushed before each."""
+    call = lambda: run_op(w)  # noqa: E731
+    if GRAPH_REPLAY:
+        # warm the op (workspace, attributes) on a side stream, then capture one call; a replay
+        # puts the op's launches on the stream without the host-side launch path
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                run_op(w)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run_op(w)
+        call = graph.replay
+    return _time_calls(call, steps, warmup, dist_on, flush)
+
+
+def _time_calls(run, steps: int, warmup: int, dist_on: bool, flush):
     for _ in range(warmup):
         flush.zero_()
-        run_op(w)
+        run()
     barrier(dist_on)
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     for i in range(steps):
         flush.zero_()
         starts[i].record()
-        run_op(w)
+        run()
         ends[i].record()
     barrier(dist_on)
     per = [s.elapsed_time(e) for s, e in zip(starts, ends)]
@@ -473,6 +494,8 @@ def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, pea
            "algorithmic_bytes": w.algorithmic_bytes(), "algorithmic_flops": w.algorithmic_flops(),
            "gpu_launches": launches_per_step(w) * steps,
            "l2": "inputs larger than L2" if big else "flushed between steps (256 MiB write)"}
+    if GRAPH_REPLAY:
+        res["cuda_graph"] = "each step replays one captured operator call"
     if with_e2e:
         e_steps = max(3, min(steps, 50))
         ms, bi, bo = time_e2e(w, device, e_steps, min(warmup, 5), dist_on, world)
@@ -528,7 +551,8 @@ def run_ours(args):
                        "l2": main["l2"], "page_size": 16, "index_granularity": "per-token slot ids",
                        "median_ms": main["median_ms"], "min_ms": main["min_ms"],
                        "algorithmic_flops_per_step": main["algorithmic_flops"],
-                       "algorithmic_bytes_per_step": main["algorithmic_bytes"]},
+                       "algorithmic_bytes_per_step": main["algorithmic_bytes"],
+                       **({"cuda_graph": main["cuda_graph"]} if "cuda_graph" in main else {})},
             "clocks": clocks.summary(), "e2e": main.get("e2e"), "gpu_launches": main["gpu_launches"],
             "roofline": main["roofline"], "cpu_baseline": cpu,
         }
@@ -722,14 +746,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-decode", action="store_true", help="skip the cfg5a decode measurement")
+    ap.add_argument("--graph", action="store_true",
+                    help="kernel timing replays a CUDA graph of one operator call (launch overhead apart)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the configuration's batch size (small profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    global BATCH_OVERRIDE
+    global BATCH_OVERRIDE, GRAPH_REPLAY
     BATCH_OVERRIDE = args.batch
+    GRAPH_REPLAY = args.graph
     if args.workload == "qk_norm_rope_store":
         run_pre_attention_step(args)
     elif args.workload == "store_kv_cache":
