@@ -174,3 +174,26 @@ def test_cfg5a_reduced_and_properties():
     tuned = torch.tensor(compute_num_kv_splits(w.kv_lens, w.hkv), dtype=torch.int32).cuda()
     out2 = run(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, tuned, 32)
     assert (out.float() - out2.float()).abs().max() <= 1.6e-2
+
+
+def test_cfg5a_full_size_properties():
+    """The long-context decode batch at its full size (256 sequences, 38 GB of K/V), checked through
+    properties that need no full-size oracle: the result does not depend on the split counts beyond
+    rounding, doubling V doubles the output bit for bit (a power-of-two factor commutes with every
+    rounding on the path), and the shortest, median and longest sequences agree with the oracle."""
+    from mini_sglang_mlx_b200 import synthetic as S
+    from mini_sglang_mlx_b200.attention import compute_num_kv_splits
+    w = S.cfg5a_decode()
+    tuned = torch.tensor(compute_num_kv_splits(w.kv_lens, w.hkv), dtype=torch.int32).cuda()
+    out = run(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, tuned, w.max_kv_splits)
+    assert torch.isfinite(out.float()).all()
+    ref_splits = run(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, w.num_kv_splits, w.max_kv_splits)
+    assert (out.float() - ref_splits.float()).abs().max() <= 1.6e-2
+    order = sorted(range(w.batch), key=lambda b: w.kv_lens[b])
+    pick = [order[0], order[len(order) // 2], order[-1]]
+    ref = O.paged_decode_attention_oracle(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices,
+                                          w.sm_scale, seqs=pick)
+    assert_close_to_oracle(out[pick], ref[pick], "cfg5a full size, subsample")
+    w.v_cache.mul_(2)
+    doubled = run(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, tuned, w.max_kv_splits)
+    assert torch.equal(doubled, out * 2)

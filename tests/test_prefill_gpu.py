@@ -215,3 +215,23 @@ def test_head_dim_256_one_query_token_equals_the_decode_op():
     out_d = paged_decode_attention(d["q"], d["k_cache"], d["v_cache"], d["kv_indptr"], d["kv_indices"], splits,
                                    1 / math.sqrt(256), 8)
     assert (out_p.float() - out_d.float()).abs().max().item() <= 2e-2
+
+
+def test_cfg5b_largest_point_properties():
+    """Chunk 4096 over a cached prefix of 32768 tokens (the largest grid point): the first and the
+    last 64 query tokens against the oracle (as 64-token chunks behind a longer prefix: the same
+    rows of the same problem), and doubling V doubles the output bit for bit."""
+    from mini_sglang_mlx_b200 import synthetic as S
+    w = S.cfg5b_prefill_point(4096, 32768)
+    out = _run_workload(w)
+    assert torch.isfinite(out.float()).all()
+    n = 64
+    for first in (0, 4096 - n):
+        qo = torch.tensor([0, n], dtype=torch.int32, device=out.device)
+        kvp = torch.tensor([0, 32768 + first + n], dtype=torch.int32, device=out.device)
+        pre = torch.tensor([32768 + first], dtype=torch.int32, device=out.device)
+        ref = O.paged_prefill_attention_oracle(w.q[first:first + n], w.k_cache, w.v_cache, qo, kvp,
+                                               w.kv_indices[: 32768 + first + n], pre, w.sm_scale)
+        assert_close_to_oracle(out[first:first + n], ref, f"cfg5b 4096x32768 rows {first}..")
+    w.v_cache.mul_(2)
+    assert torch.equal(_run_workload(w), out * 2)
