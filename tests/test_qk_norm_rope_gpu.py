@@ -165,3 +165,25 @@ def test_backend_forward_from_projections_equals_norm_rope_then_forward():
         assert_close_to_oracle(out_f, out_p.float().cpu(), f"fused layer {phase}")
         for r in reqs:
             r.complete_one()
+
+
+def test_fused_step_into_a_pool_beyond_4_gib_per_tensor():
+    """K/V rows scattered to slots whose byte offset needs more than 32 bits."""
+    from mini_sglang_mlx_b200 import qk_norm_rope_store
+    n, hq, hkv, d, S = 6, 16, 8, 128, 2_300_000
+    _, q, k, v, qw, kw, pos, _, _, _ = _case(n, hq, hkv, torch.bfloat16, seed=3, max_pos=50000, num_slots=64)
+    loc = torch.tensor([S - 1, 2_097_152, 2_097_999, 2_250_000, 0, 1_048_576], dtype=torch.int32)
+    small_k = torch.zeros(8, hkv, d, dtype=torch.bfloat16)       # the oracle scatters into a dense pool
+    kc_ref, vc_ref = small_k.clone(), small_k.clone()
+    q_ref = qk_norm_rope_store_oracle(q, k, v, qw, kw, pos, torch.arange(n, dtype=torch.int32), kc_ref, vc_ref,
+                                      rope_base=1e6, eps=1e-6, rotary_dim=d)
+    kcd = torch.zeros(S, hkv, d, dtype=torch.bfloat16, device="cuda")
+    vcd = torch.zeros_like(kcd)
+    out = qk_norm_rope_store(q.cuda(), k.cuda(), v.cuda(), qw.cuda(), kw.cuda(), pos.cuda(), loc.cuda(),
+                             kcd, vcd, rope_base=1e6, eps=1e-6, rotary_dim=d)
+    torch.cuda.synchronize()
+    _check(out, q_ref, "q")
+    rows = loc.long().cuda()
+    _check(kcd[rows], kc_ref[:n], "k rows")
+    assert torch.equal(vcd[rows].cpu(), vc_ref[:n])
+    assert int((kcd != 0).any(dim=(1, 2)).sum()) == n and int((vcd != 0).any(dim=(1, 2)).sum()) == n

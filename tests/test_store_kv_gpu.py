@@ -140,3 +140,21 @@ def test_backend_prefill_then_decode_steps_match_the_oracle():
             r.complete_one()
     assert torch.equal(pool.k_cache(layer).cpu(), kc) and torch.equal(pool.v_cache(layer).cpu(), vc)
     assert torch.count_nonzero(pool.k_cache(0)) == 0
+
+
+def test_scatter_into_a_pool_beyond_4_gib_per_tensor():
+    """Slot ids whose byte offset does not fit in 32 bits (the reference's 32-bit offset
+    arithmetic overflows past 2 M slots of 2 KB): rows land where they should, their
+    neighbours and the low alias of each offset stay zero."""
+    from mini_sglang_mlx_b200 import store_kv_cache
+    hkv, d, S = 8, 128, 2_300_000                       # 4.7 GB per tensor
+    kc = torch.zeros(S, hkv, d, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    g = torch.Generator().manual_seed(9)
+    idx = torch.tensor([S - 1, 2_097_152, 2_097_153 + 77, 2_200_000, 5], dtype=torch.int32)
+    k = torch.randn(len(idx), hkv, d, generator=g).bfloat16().cuda()
+    v = torch.randn(len(idx), hkv, d, generator=g).bfloat16().cuda()
+    store_kv_cache(kc, vc, idx.cuda(), k, v)
+    torch.cuda.synchronize()
+    assert torch.equal(kc[idx.long().cuda()], k) and torch.equal(vc[idx.long().cuda()], v)
+    assert int((kc != 0).any(dim=(1, 2)).sum()) == len(idx) and int((vc != 0).any(dim=(1, 2)).sum()) == len(idx)
