@@ -338,7 +338,40 @@ class E2EPipeline:
             s.synchronize()
 
 
+def bind_near_gpu(index: int):
+    """Restrict this process to the CPUs NVML names as local to GPU `index` (those among the
+    CPUs it may use), so that the pinned staging buffers allocated next are placed on the
+    GPU's NUMA node.  Returns (previous affinity, note); the caller restores the affinity."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        allowed = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (max(allowed) + 64) // 64)
+        near = {64 * i + b for i, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus = near & allowed
+        if not cpus or cpus == allowed:
+            return None, "all usable CPUs are equally near" if cpus else "no usable CPU near the GPU"
+        os.sched_setaffinity(0, cpus)
+        return allowed, f"{len(cpus)} of {len(allowed)} CPUs"
+    except Exception as e:  # noqa: BLE001
+        return None, f"unavailable ({type(e).__name__})"
+
+
+NUMA_NOTE = None
+
+
 def time_e2e(w, device, steps, warmup, dist_on, world):
+    global NUMA_NOTE
+    previous, NUMA_NOTE = bind_near_gpu(device.index)
+    try:
+        return _time_e2e(w, device, steps, warmup, dist_on, world)
+    finally:
+        if previous is not None:
+            os.sched_setaffinity(0, previous)
+
+
+def _time_e2e(w, device, steps, warmup, dist_on, world):
     be, batch, host, dev = build_e2e(w, device)
     gather = None
     if dist_on and world > 1:
@@ -502,7 +535,7 @@ def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, pea
         ms = max_over_ranks(ms, dist_on)
         res["e2e"] = {"value": work_all * e_steps / (ms * 1e-3) / div, "unit": unit,
                       "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo, "steps": e_steps,
-                      "ms_per_step": ms / e_steps,
+                      "ms_per_step": ms / e_steps, "cpu_binding": NUMA_NOTE,
                       "pipelining": "copies and compute of neighbouring steps overlap "
                                     "(3 streams, 2 buffers); one host wait per step"}
     return w, res
