@@ -119,9 +119,19 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- workloads
 BATCH_OVERRIDE = None  # --batch: smaller batch of the same configuration (profiling captures)
+INDEX = "page"         # --index: "page" = one id per 16-token page (the *_p16 operators, K/V tiles
+                       # fetched as TMA boxes); "token" = the reference's per-token slot ids
 
 
 def make_workload(name: str, device, rank: int):
+    w = _make_workload(name, device, rank)
+    w.index = INDEX
+    if INDEX == "page":
+        w.page_indptr, w.page_indices, w.kv_lens_dev = w.page_csr()
+    return w
+
+
+def _make_workload(name: str, device, rank: int):
     from mini_sglang_mlx_b200 import synthetic as S
     seed_shift = 0 * rank  # every rank runs the same batch shape and lengths: fixed work per GPU
     kw = {} if BATCH_OVERRIDE is None else {"batch": BATCH_OVERRIDE}
@@ -150,7 +160,16 @@ def make_workload(name: str, device, rank: int):
 
 
 def run_op(w):
-    from mini_sglang_mlx_b200 import paged_decode_attention, paged_prefill_attention
+    from mini_sglang_mlx_b200 import (paged_decode_attention, paged_decode_attention_p16,
+                                      paged_prefill_attention, paged_prefill_attention_p16)
+    if w.index == "page":
+        if w.kind == "decode":
+            return paged_decode_attention_p16(w.q, w.k_cache, w.v_cache, w.page_indptr, w.page_indices,
+                                              w.kv_lens_dev, w.num_kv_splits, w.sm_scale, w.max_kv_splits)
+        return paged_prefill_attention_p16(w.q, w.k_cache, w.v_cache, w.qo_indptr, w.page_indptr,
+                                           w.page_indices, w.kv_lens_dev, w.prefix_lens, w.sm_scale,
+                                           w.max_len_extend, is_cross_attention=w.is_cross_attention,
+                                           sliding_window_size=w.sliding_window_size)
     if w.kind == "decode":
         return paged_decode_attention(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices,
                                       w.num_kv_splits, w.sm_scale, w.max_kv_splits)
@@ -164,7 +183,8 @@ def launches_per_step(w) -> int:
     from mini_sglang_mlx_b200 import _lib
     if w.kind == "decode":
         return 2
-    need = _lib.lib().msgl_prefill_workspace_bytes(w.batch, w.q.shape[0], w.kv_indices.numel(), w.hq,
+    total_kv = w.page_indices.numel() * 16 if w.index == "page" else w.kv_indices.numel()
+    need = _lib.lib().msgl_prefill_workspace_bytes(w.batch, w.q.shape[0], total_kv, w.hq,
                                                    w.hkv, w.head_dim, w.max_len_extend,
                                                    w.sliding_window_size)
     return 2 if need > 256 else 1
@@ -581,7 +601,9 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": main["workload"], "sharding": "by request, one batch per GPU",
-                       "l2": main["l2"], "page_size": 16, "index_granularity": "per-token slot ids",
+                       "l2": main["l2"], "page_size": 16,
+                       "index_granularity": ("one id per 16-token page (TMA box loads)" if INDEX == "page"
+                                             else "per-token slot ids"),
                        "median_ms": main["median_ms"], "min_ms": main["min_ms"],
                        "algorithmic_flops_per_step": main["algorithmic_flops"],
                        "algorithmic_bytes_per_step": main["algorithmic_bytes"],
@@ -791,11 +813,15 @@ def main():
                     help="kernel timing replays a CUDA graph of one operator call (launch overhead apart)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
+    ap.add_argument("--index", default="page", choices=["page", "token"],
+                    help="kernel-only timing through the page-granular operators (one id per 16-token "
+                         "page) or the per-token ones; the end-to-end leg always runs AttnBackend")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the configuration's batch size (small profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    global BATCH_OVERRIDE, GRAPH_REPLAY
+    global BATCH_OVERRIDE, GRAPH_REPLAY, INDEX
+    INDEX = args.index
     BATCH_OVERRIDE = args.batch
     GRAPH_REPLAY = args.graph
     if args.workload == "qk_norm_rope_store":

@@ -3,9 +3,22 @@
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream
  * handle (passed as void*, i.e. a cudaStream_t).  No entry point retains a
- * pointer past the call, synchronises the host with the device, or allocates
- * device memory: scratch space is supplied by the caller (query its size with
- * the *_workspace_bytes functions).  Launches are asynchronous on `stream`.
+ * pointer past the call or allocates device memory, and none but
+ * msgl_read_status synchronises the host with the device: scratch space is
+ * supplied by the caller (query its size with the *_workspace_bytes
+ * functions; msgl_paged_decode_attention_static uses an array inside the
+ * library instead).  Launches are asynchronous on `stream`.
+ *
+ * Workspaces.  A workspace starts with a header of MSGL_WORKSPACE_HEADER_BYTES.
+ * Its first word is a sticky device status (0 = fine, 1 = a bounded wait inside
+ * a kernel ran out, 2 = a slot or page id outside the pool, or a length beyond
+ * a sequence's pages, was met: such rows are read as zero keys and values).
+ * From byte 256 on it holds the arrival counters of the attention ops'
+ * split-KV pieces (the piece that arrives last merges the partials).  The
+ * kernels leave the counters at zero, but they must BE zero at the first call:
+ * clear at least the header once after allocating a workspace
+ * (cudaMemsetAsync), use one workspace per stream, and let nothing else write
+ * to the header.  After a call that reported status 1 clear it again.
  *
  * Each function replaces one operator of the reference extension
  * `mini_sglang_mlx_kernel` (mini-sglang-mlx-kernel/csrc/bindings.cpp); the
@@ -32,7 +45,7 @@
 extern "C" {
 #endif
 
-#define MSGL_ABI_VERSION 1
+#define MSGL_ABI_VERSION 2
 
 /* Status codes returned by every int-valued entry point. */
 enum {
@@ -49,6 +62,10 @@ enum {
 /* Element types of q / k_cache / v_cache / out. */
 enum { MSGL_DTYPE_BF16 = 0, MSGL_DTYPE_F16 = 1 };
 
+/* Bytes of the header every workspace starts with: status word (256 bytes) and 16384
+ * arrival counters. */
+#define MSGL_WORKSPACE_HEADER_BYTES (256 + 16384 * 4)
+
 /* Largest split count the decode workspace layout supports. */
 #define MSGL_MAX_KV_SPLITS 128
 
@@ -61,9 +78,11 @@ const char* msgl_last_error_string(void);
 int msgl_device_sm_count(void);
 
 /*
- * Bytes of scratch the decode op needs: fp32 partial outputs
- * (batch, num_q_heads, max_kv_splits, head_dim) followed by fp32 log-sum-exp
- * (batch, num_q_heads, max_kv_splits).
+ * Bytes of scratch the decode op needs: the header, fp32 partial outputs
+ * (batch, num_q_heads, max_kv_splits, head_dim) and fp32 log-sum-exp (batch,
+ * num_q_heads, max_kv_splits); a batch of more than 16384 (sequence, head)
+ * pairs gets a counter region of its own in front of the partials, which every
+ * call clears.
  * Replaces the two temporaries of PagedDecodeAttention::eval_gpu
  * (mini-sglang-mlx-kernel/csrc/paged_decode_attention.cpp:119-131).
  */
@@ -71,7 +90,8 @@ size_t msgl_decode_workspace_bytes(int batch, int num_q_heads, int head_dim, int
 
 /*
  * Paged decode attention: one query token per sequence over all of its KV
- * tokens, split-KV partial pass plus log-sum-exp merge pass.
+ * tokens, split over the KV range; the piece of a (sequence, KV head) that
+ * finishes last merges the partials by log-sum-exp (one launch).
  * Replaces paged_decode_attention
  * (mini-sglang-mlx-kernel/csrc/paged_decode_attention.cpp:15-73, binding
  * csrc/bindings.cpp:36-44) and its two Metal stages
@@ -109,12 +129,28 @@ int msgl_paged_decode_attention(
  *  - All calls on a device share the one array and it keeps the previous
  *    call's contents; calls that overlap on the GPU (different streams) race
  *    on it, so issue them on one stream or order them with events.
+ *  - The array is laid out like a workspace (status word, arrival counters,
+ *    partials); it is zero when the library is loaded.  Read its status word
+ *    with msgl_read_status(NULL, ...).  The cached device address belongs to
+ *    the device's primary context: after cudaDeviceReset the library has to
+ *    be loaded afresh.
  */
 int msgl_paged_decode_attention_static(
     const void* q, const void* k_cache, const void* v_cache,
     const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* num_kv_splits,
     void* out, int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t num_slots,
     int dtype, float sm_scale, int max_kv_splits, void* stream);
+
+/*
+ * Reads the sticky device status word of `workspace` (NULL: of the array behind
+ * msgl_paged_decode_attention_static on the current device): waits for the work
+ * queued on `stream`, copies the word to the host, clears it on the device if
+ * `clear` is non-zero.  Returns MSGL_OK if it was 0, else MSGL_DEVICE_STATUS with
+ * a message that names the condition; *status_out (may be NULL) receives the raw
+ * word.  The only entry point that waits for the device.  No counterpart in the
+ * reference (its kernels do not check slot ids).
+ */
+int msgl_read_status(void* workspace, int clear, int* status_out, void* stream);
 
 /*
  * msgl_paged_decode_attention with the output gate of the reference's Qwen3.5 attention
@@ -176,6 +212,9 @@ int msgl_paged_prefill_attention_gated(
 /*
  * Scatter new keys/values into the pool: k_cache[indices[r]] = k[r],
  * v_cache[indices[r]] = v[r] for r < length.  Row strides are in elements.
+ * A row whose index is outside [0, num_slots) is dropped; if status_word (a
+ * device int, e.g. the head of a workspace; may be NULL) is given it is set
+ * to 2 then.
  * Replaces store_kv_cache
  * (mini-sglang-mlx-kernel/csrc/store_kv_cache.cpp:13-107, kernel
  * csrc/store_kv_cache.metal:7-31).
@@ -183,20 +222,23 @@ int msgl_paged_prefill_attention_gated(
 int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, const void* k,
                         const void* v, int length, int num_kv_heads, int head_dim,
                         int64_t num_slots, int64_t cache_row_stride, int64_t input_row_stride,
-                        int dtype, void* stream);
+                        int dtype, void* status_word, void* stream);
 
 /*
  * CSR metadata from a page table: for sequence b, copies
  * page_table[table_idx[b], 0:kv_lens[b]] to kv_indices[kv_indptr[b]:...]
  * in one launch.  kv_indptr (batch+1) must already hold the exclusive prefix
- * sum of kv_lens.
+ * sum of kv_lens.  The table has table_rows x table_cols entries and the
+ * output total_kv: a row id, a length or an output position outside them is
+ * skipped (clamped) and sets status_word (a device int, may be NULL) to 2.
  * Replaces the per-request slice-and-concatenate loops of
  * AttnBackend.build_prefill_metadata / build_decode_metadata
  * (mini_sglang_mlx/attention/backend.py:239-244, 279-284).
  */
 int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
                            const int32_t* table_idx, const int32_t* kv_indptr,
-                           int32_t* kv_indices, int batch, int64_t total_kv, void* stream);
+                           int32_t* kv_indices, int batch, int64_t total_kv, int64_t table_rows,
+                           int64_t table_cols, void* status_word, void* stream);
 
 /*
  * Page-granular index entries.  The reference hard-wires one token per page
@@ -205,11 +247,18 @@ int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
  * allocated in pages of page_size tokens (slot = page * page_size + offset) is
  * described more compactly by one id per PAGE: page_indptr (batch+1),
  * page_indices (total_pages) and the token lengths kv_lens (batch), all int32
- * device arrays.  These entries take that form; they build kv_indptr and the
- * per-token slot ids on the device (a scan of the lengths and one 4-byte store
- * per token, in front of the same kernels) and then run the op above.
- * A length that is negative or exceeds page_size * (pages of the sequence)
- * sets the device status word to 2 and is clamped.
+ * device arrays.  These entries take that form.  With a page size that is a
+ * multiple of 16 they are the fast path: the 16 token rows of a page (or of a
+ * 16-row slice of a larger page) are contiguous in the pool, and the kernels
+ * fetch them as TMA box copies (16 rows x 64 elements, 128-byte swizzle, one
+ * instruction per box, completion counted on an mbarrier) straight from the
+ * page ids; the query tile of the prefill op is fetched the same way.  Other
+ * page sizes build kv_indptr and the per-token slot ids on the device first (a
+ * scan of the lengths and one 4-byte store per token) and run the per-token
+ * kernels.  A length that is negative or exceeds page_size * (pages of the
+ * sequence) sets the device status word to 2 and is clamped; so does a page id
+ * outside the pool, whose rows then read as zeros.  The pools must be 16-byte
+ * aligned.
  *
  * Workspace: the op's own scratch followed by the index scratch,
  *   decode : round_up(msgl_decode_workspace_bytes(...), 256)

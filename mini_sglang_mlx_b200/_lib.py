@@ -34,6 +34,7 @@ SIGNATURES = {
              _i, _f, _i, _i, _i, _vp]),
     "msgl_paged_decode_attention_static": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _f, _i, _vp]),
+    "msgl_read_status": (_i, [_vp, _i, _vp, _vp]),
     "msgl_prefill_workspace_bytes": (_sz, [_i, _i, _i64, _i, _i, _i, _i, _i]),
     "msgl_page_index_workspace_bytes": (_sz, [_i, _i64, _i]),
     "msgl_paged_decode_attention_p16": (
@@ -46,8 +47,8 @@ SIGNATURES = {
     "msgl_paged_prefill_attention": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i64, _i, _i, _i, _i64,
              _i, _f, _i, _i, _i, _vp]),
-    "msgl_store_kv_cache": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
-    "msgl_gather_kv_indices": (_i, [_vp, _i64, _vp, _vp, _vp, _i, _i64, _vp]),
+    "msgl_store_kv_cache": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
+    "msgl_gather_kv_indices": (_i, [_vp, _i64, _vp, _vp, _vp, _i, _i64, _i64, _i64, _vp, _vp]),
     "msgl_fast_compare_key": (_i64, [_vp, _vp, _i64, _i64, _i]),
     "msgl_qk_norm_rope_store": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i64, _i64,

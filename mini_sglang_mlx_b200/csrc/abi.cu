@@ -1,11 +1,13 @@
 // C-ABI entry points of the B200 paged-attention library: argument
 // validation (same rules and message prefixes as the reference host wrappers),
 // scratch layout, launch configuration.  Declarations: include/msgl_b200.h.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -28,7 +30,11 @@ int cuda_fail(const char* op, cudaError_t e) {
   return fail(MSGL_CUDA_ERROR, std::string(op) + ": CUDA error: " + cudaGetErrorString(e));
 }
 
-constexpr size_t kStatusBytes = 256;  // head of every workspace: device status word
+// Head of every workspace: the device status word (first 256 bytes), then kTicketSlots arrival
+// counters of split-KV pieces at a fixed place, so that a buffer re-used by calls of different
+// shapes never finds anything but the zeros the kernels leave there.
+constexpr size_t kTicketSlots = 16384;
+constexpr size_t kStatusBytes = 256 + kTicketSlots * sizeof(int);
 
 // Scratch of msgl_paged_decode_attention_static: lives in the library's image,
 // so every GPU that loads the library holds these bytes until the process exits.
@@ -81,6 +87,89 @@ int sm_count_cached() {
 template <typename K>
 cudaError_t allow_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+// ---- TMA tensor maps over a K or V pool (page-granular entries)
+// The encoder is a driver-API function; it is looked up through the runtime, so the library
+// needs no link against libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// 2-D map over a pool (num_slots rows of num_kv_heads * head_dim 16-bit elements): a box is
+// 16 token rows x 64 elements (128 bytes) of one head, written to shared memory with the
+// 128-byte swizzle, i.e. in the layout the tensor-core descriptors of the kernels expect.
+// Rows outside the pool read as zeros.  The last map per (pointer, shape) is kept per thread.
+bool make_pool_tensor_map(CUtensorMap* out, const void* base, int64_t num_slots, int num_kv_heads,
+                          int head_dim, int dtype) {
+  struct Cached {
+    const void* base;
+    int64_t num_slots;
+    int hkv, hd, dtype;
+    CUtensorMap map;
+  };
+  static thread_local Cached cache[4] = {};
+  static thread_local int next = 0;
+  for (const Cached& c : cache)
+    if (c.base == base && c.num_slots == num_slots && c.hkv == num_kv_heads && c.hd == head_dim &&
+        c.dtype == dtype && base != nullptr) {
+      *out = c.map;
+      return true;
+    }
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc || num_slots <= 0 || reinterpret_cast<uintptr_t>(base) % 16 != 0) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(num_kv_heads) * head_dim,
+                              static_cast<cuuint64_t>(num_slots)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(num_kv_heads) * head_dim * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(msgl::kTmaBoxRows)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = enc(&m, dtype == MSGL_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  cache[next] = Cached{base, num_slots, num_kv_heads, head_dim, dtype, m};
+  next = (next + 1) % 4;
+  *out = m;
+  return true;
+}
+
+// 3-D map over the query tensor (tokens, query heads, head_dim): a box is 64 elements x the
+// `group` heads of one KV head x 128 / group tokens, i.e. the 128 packed rows of a query
+// sub-tile in the order the kernel numbers them.  Needs a group that divides 128.
+bool make_query_tensor_map(CUtensorMap* out, const void* q, int total_q, int num_q_heads, int group,
+                           int head_dim, int dtype) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc || total_q <= 0 || group <= 0 || 128 % group != 0 || num_q_heads % group != 0 ||
+      reinterpret_cast<uintptr_t>(q) % 16 != 0)
+    return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(num_q_heads),
+                              static_cast<cuuint64_t>(total_q)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2,
+                                 static_cast<cuuint64_t>(num_q_heads) * head_dim * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(group), static_cast<cuuint32_t>(128 / group)};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = enc(out, dtype == MSGL_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         3, const_cast<void*>(q), dims, strides, box, elem_strides,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
 }
 
 // Launches `kernel` so that its CTAs may be scheduled while the previous kernel of the
@@ -140,7 +229,7 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
   pl.kv_chunk = 0;
   // Split the key range only when the query tiles fill at most half of the CTA slots: a
   // nearly full single wave beats more, shorter CTAs plus a merge pass.
-  if (qtiles * hkv * 2 <= slots && visible > 0) {
+  if (qtiles * hkv * 2 <= slots && qtiles * hkv <= msgl::kPrefillTickets && visible > 0) {
     // One wave: every (sequence, head, query tile) unit is cut into as many equal pieces as
     // the CTA slots allow for a sequence of average length.  Measured on the draft-block and
     // verify configurations and on the small-chunk points of the prefill grid (chunk x prefix
@@ -154,12 +243,19 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
     chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
   }
+#ifdef MSGL_TRACE
+  // development builds only: a key-range piece length to try instead of the policy's
+  if (const char* env = std::getenv("MSGL_KV_CHUNK")) {
+    const int forced = std::atoi(env);
+    if (forced >= 0) pl.kv_chunk = forced / 128 * 128;
+  }
+#endif
   pl.items = msgl::prefill_item_bound(batch, total_q, total_kv, G, BM, max_len_extend, pl.kv_chunk);
   if (pl.kv_chunk > 0) {
     const size_t slots_n = static_cast<size_t>(pl.items) * hkv;
     pl.part_o_bytes = slots_n * BM * head_dim * sizeof(float);
     pl.part_ml_bytes = slots_n * BM * 2 * sizeof(float);
-    pl.plan_bytes = (static_cast<size_t>(batch) * 2 * sizeof(int) + 255) / 256 * 256;
+    pl.plan_bytes = 0;
   }
   return pl;
 }
@@ -190,15 +286,30 @@ __global__ void store_kv_kernel(unsigned char* __restrict__ kc, unsigned char* _
   }
 }
 
+// Rows and columns of the table and the size of the output are checked: a table row id outside
+// [0, num_rows), a length beyond num_cols or an output position beyond total_kv is skipped and
+// reported (status word 2) instead of being dereferenced.
 __global__ void gather_kv_indices_kernel(const int32_t* __restrict__ page_table,
                                          int64_t row_stride, const int32_t* __restrict__ table_idx,
                                          const int32_t* __restrict__ kv_indptr,
-                                         int32_t* __restrict__ kv_indices, int batch) {
+                                         int32_t* __restrict__ kv_indices, int batch,
+                                         int64_t num_rows, int64_t num_cols, int64_t total_kv,
+                                         int* status) {
   const int b = blockIdx.y;
-  const int begin = kv_indptr[b];
-  const int len = kv_indptr[b + 1] - begin;
-  const int32_t* row = page_table + static_cast<int64_t>(table_idx[b]) * row_stride;
-  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < len; t += gridDim.x * blockDim.x)
+  const int64_t begin = kv_indptr[b];
+  int64_t len = static_cast<int64_t>(kv_indptr[b + 1]) - begin;
+  const int64_t r = table_idx[b];
+  bool bad = begin < 0 || len < 0 || r < 0 || r >= num_rows;
+  if (!bad && (len > num_cols || begin + len > total_kv)) {
+    len = max(static_cast<int64_t>(0), min(num_cols, total_kv - begin));
+    if (status && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(status, 2);
+  }
+  if (bad) {
+    if (status && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(status, 2);
+    return;
+  }
+  const int32_t* row = page_table + r * row_stride;
+  for (int64_t t = blockIdx.x * blockDim.x + threadIdx.x; t < len; t += gridDim.x * blockDim.x)
     kv_indices[begin + t] = row[t];
 }
 
@@ -244,47 +355,81 @@ __global__ void __launch_bounds__(1024) page_lens_scan_kernel(const int32_t* __r
   }
 }
 
+// A page id whose slots would fall outside [0, num_slots) gives slot id -1 (the attention
+// kernels read such a row as zeros and report it); the slot is computed in 64 bits so that a
+// corrupt id cannot wrap into the pool.
 __global__ void expand_page_indices_kernel(const int32_t* __restrict__ page_indptr,
                                            const int32_t* __restrict__ page_indices,
                                            const int32_t* __restrict__ kv_indptr, int page_size,
-                                           int32_t* __restrict__ kv_indices) {
+                                           int64_t total_pages, int64_t num_slots,
+                                           int32_t* __restrict__ kv_indices, int* status) {
   const int b = blockIdx.y;
   const int begin = kv_indptr[b];
   const int len = kv_indptr[b + 1] - begin;
-  const int32_t* pages = page_indices + page_indptr[b];
+  const int64_t first = page_indptr[b];
+  if (first < 0 || first > total_pages) {
+    if (status && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(status, 2);
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < len; t += gridDim.x * blockDim.x)
+      kv_indices[begin + t] = -1;
+    return;
+  }
+  const int32_t* pages = page_indices + first;
   for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < len; t += gridDim.x * blockDim.x) {
     const int pg = t / page_size;
-    kv_indices[begin + t] = pages[pg] * page_size + (t - pg * page_size);
+    int64_t slot = -1;
+    if (first + pg < total_pages) slot = static_cast<int64_t>(pages[pg]) * page_size + (t - pg * page_size);
+    if (slot < 0 || slot >= num_slots) {
+      if (status) atomicExch(status, 2);
+      slot = -1;
+    }
+    kv_indices[begin + t] = static_cast<int32_t>(slot);
   }
 }
 
 template <typename T>
-int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s) {
+int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s, const CUtensorMap& tm_k,
+                  const CUtensorMap& tm_v) {
   dim3 grid1(p.max_splits, p.hkv, p.batch);
-  dim3 grid2(p.hq, p.batch);
+  const bool paged = p.kv_lens != nullptr;
+  auto launch = [&](auto k1, int smem) -> int {
+    cudaError_t e = allow_smem(k1, smem);
+    if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
+    k1<<<grid1, kDecWarps * 32, smem, s>>>(p, tm_k, tm_v);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
+    return MSGL_OK;
+  };
+  // page-granular: the same ring plus the slack that puts it on a 1024-byte boundary
   if (head_dim == 128) {
-    auto k1 = msgl::decode_partial_kernel<T, 128, kDecWarps, kDecStages>;
     constexpr int smem = kDecWarps * kDecStages * 2 * msgl::kDecodeGroupTokens * 256;
-    cudaError_t e = allow_smem(k1, smem);
-    if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
-    k1<<<grid1, kDecWarps * 32, smem, s>>>(p);
-    launch_dependent(msgl::decode_merge_kernel<T, 128, kDecCtaTokens>, grid2, dim3(128), s, p);
-  } else {
-    // head_dim 256: 512-byte token rows, two ring stages per warp (128 KB per CTA)
-    constexpr int kStages256 = 2;
-    auto k1 = msgl::decode_partial_kernel<T, 256, kDecWarps, kStages256>;
-    constexpr int smem = kDecWarps * kStages256 * 2 * msgl::kDecodeGroupTokens * 512;
-    cudaError_t e = allow_smem(k1, smem);
-    if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
-    k1<<<grid1, kDecWarps * 32, smem, s>>>(p);
-    launch_dependent(msgl::decode_merge_kernel<T, 256, kDecCtaTokens>, grid2, dim3(256), s, p);
+    return paged ? launch(msgl::decode_partial_kernel<T, 128, kDecWarps, kDecStages, true>, smem + 1024)
+                 : launch(msgl::decode_partial_kernel<T, 128, kDecWarps, kDecStages>, smem);
   }
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
-  return MSGL_OK;
+  // head_dim 256: 512-byte token rows, two ring stages per warp (128 KB per CTA)
+  constexpr int kStages256 = 2;
+  constexpr int smem = kDecWarps * kStages256 * 2 * msgl::kDecodeGroupTokens * 512;
+  return paged ? launch(msgl::decode_partial_kernel<T, 256, kDecWarps, kStages256, true>, smem + 1024)
+               : launch(msgl::decode_partial_kernel<T, 256, kDecWarps, kStages256>, smem);
 }
 
+// Page-granular addressing of a call (null: per-token kv_indptr / kv_indices).
+struct PageIndex {
+  const int32_t* page_indptr;
+  const int32_t* page_indices;
+  const int32_t* kv_lens;
+  int page_size;
+};
+
 }  // namespace
+
+// Arrival counters of the decode op: one per (sequence, KV head).  They sit in the workspace
+// header when there are at most kTicketSlots of them; a larger batch gets a region of its own
+// behind the header, cleared by every call (the workspace query is not told the KV head
+// count, so it sizes that region for the query heads).
+static size_t decode_ticket_bytes(int batch, int num_q_heads) {
+  const size_t n = static_cast<size_t>(batch) * num_q_heads;
+  return n <= kTicketSlots ? 0 : (n * sizeof(int) + 255) / 256 * 256;
+}
 
 extern "C" {
 
@@ -297,7 +442,8 @@ int msgl_device_sm_count(void) { return sm_count_cached(); }
 size_t msgl_decode_workspace_bytes(int batch, int num_q_heads, int head_dim, int max_kv_splits) {
   if (batch <= 0 || num_q_heads <= 0 || head_dim <= 0 || max_kv_splits <= 0) return kStatusBytes;
   const size_t rows = static_cast<size_t>(batch) * num_q_heads * max_kv_splits;
-  return kStatusBytes + rows * head_dim * sizeof(float) + rows * sizeof(float);
+  return kStatusBytes + decode_ticket_bytes(batch, num_q_heads) + rows * head_dim * sizeof(float) +
+         rows * sizeof(float);
 }
 
 static int decode_impl(const void* q, const void* k_cache, const void* v_cache,
@@ -305,7 +451,7 @@ static int decode_impl(const void* q, const void* k_cache, const void* v_cache,
                        const int32_t* num_kv_splits, const void* gate, void* out, void* workspace,
                        size_t workspace_bytes, int batch, int num_q_heads, int num_kv_heads,
                        int head_dim, int64_t num_slots, int dtype, float sm_scale,
-                       int max_kv_splits, void* stream) {
+                       int max_kv_splits, void* stream, const PageIndex* pages = nullptr) {
   const char* op = "paged_decode_attention: ";
   if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "q must be 3D (batch, num_q_heads, head_dim)");
@@ -322,8 +468,14 @@ static int decode_impl(const void* q, const void* k_cache, const void* v_cache,
   if (batch == 0) return MSGL_OK;
   if (batch > 65535 || num_kv_heads > 65535)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "batch and num_kv_heads must be <= 65535");
-  if (!q || !k_cache || !v_cache || !kv_indptr || !kv_indices || !out)
+  if (!q || !k_cache || !v_cache || !out || (!pages && (!kv_indptr || !kv_indices)))
     return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  CUtensorMap tm_k, tm_v;
+  std::memset(&tm_k, 0, sizeof(tm_k));
+  std::memset(&tm_v, 0, sizeof(tm_v));
+  if (pages && (!make_pool_tensor_map(&tm_k, k_cache, num_slots, num_kv_heads, head_dim, dtype) ||
+                !make_pool_tensor_map(&tm_v, v_cache, num_slots, num_kv_heads, head_dim, dtype)))
+    return fail(MSGL_CUDA_ERROR, std::string(op) + "cannot build the tensor maps of the K/V pool");
   const size_t need = msgl_decode_workspace_bytes(batch, num_q_heads, head_dim, max_kv_splits);
   if (!workspace || workspace_bytes < need)
     return fail(MSGL_BAD_ARG, std::string(op) + "workspace too small");
@@ -335,11 +487,26 @@ static int decode_impl(const void* q, const void* k_cache, const void* v_cache,
   p.kv_indptr = kv_indptr;
   p.kv_indices = kv_indices;
   p.num_kv_splits = num_kv_splits;
+  if (pages) {
+    p.page_indptr = pages->page_indptr;
+    p.page_indices = pages->page_indices;
+    p.kv_lens = pages->kv_lens;
+    p.page_size = pages->page_size;
+  }
   p.out = out;
   p.gate = gate;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   p.status = reinterpret_cast<int*>(ws);
-  p.part_o = reinterpret_cast<float*>(ws + kStatusBytes);
+  const size_t own_tickets = decode_ticket_bytes(batch, num_q_heads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (own_tickets == 0) {
+    p.tickets = reinterpret_cast<int*>(ws + 256);
+  } else {
+    p.tickets = reinterpret_cast<int*>(ws + kStatusBytes);
+    cudaError_t e = cudaMemsetAsync(p.tickets, 0, own_tickets, s);
+    if (e != cudaSuccess) return cuda_fail("paged_decode_attention", e);
+  }
+  p.part_o = reinterpret_cast<float*>(ws + kStatusBytes + own_tickets);
   p.part_lse = p.part_o + static_cast<size_t>(batch) * num_q_heads * max_kv_splits * head_dim;
   p.batch = batch;
   p.hq = num_q_heads;
@@ -348,9 +515,8 @@ static int decode_impl(const void* q, const void* k_cache, const void* v_cache,
   p.max_splits = max_kv_splits;
   p.num_slots = num_slots;
   p.scale_log2 = sm_scale * msgl::kLog2e;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == MSGL_DTYPE_BF16) return launch_decode<__nv_bfloat16>(p, head_dim, s);
-  return launch_decode<__half>(p, head_dim, s);
+  if (dtype == MSGL_DTYPE_BF16) return launch_decode<__nv_bfloat16>(p, head_dim, s, tm_k, tm_v);
+  return launch_decode<__half>(p, head_dim, s, tm_k, tm_v);
 }
 
 int msgl_paged_decode_attention(const void* q, const void* k_cache, const void* v_cache,
@@ -398,13 +564,36 @@ int msgl_paged_decode_attention_static(const void* q, const void* k_cache, const
   void* scratch = nullptr;
   const int rc = static_scratch_for_current_device(&scratch);
   if (rc != MSGL_OK) return rc;
-  // Nothing in the scratch has to start at zero: every partial and log-sum-exp that the
-  // merge pass reads is written by the partial pass of the same call, and the status word
-  // at its head is sticky by design (zero when the library is loaded).
+  // What has to start at zero does: the array is zero when the library is loaded, the arrival
+  // counters behind the status word are put back to zero by the CTA that merges, every partial
+  // and log-sum-exp that a merge reads is written earlier in the same call, and the status
+  // word at the head is sticky by design.
   return msgl_paged_decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, out,
                                      scratch, MSGL_STATIC_SCRATCH_BYTES, batch, num_q_heads,
                                      num_kv_heads, head_dim, num_slots, dtype, sm_scale,
                                      max_kv_splits, stream);
+}
+
+int msgl_read_status(void* workspace, int clear, int* status_out, void* stream) {
+  void* word = workspace;
+  if (!word) {
+    const int rc = static_scratch_for_current_device(&word);
+    if (rc != MSGL_OK) return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int value = 0;
+  cudaError_t e = cudaMemcpyAsync(&value, word, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess && clear) e = cudaMemsetAsync(word, 0, sizeof(int), s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return cuda_fail("read_status", e);
+  if (status_out) *status_out = value;
+  if (value == 0) return MSGL_OK;
+  return fail(MSGL_DEVICE_STATUS,
+              value == 1 ? "read_status: a bounded wait inside a kernel ran out (results are not valid)"
+              : value == 2
+                  ? "read_status: a slot or page id outside the pool, or a length beyond a sequence's "
+                    "pages, was met (those rows were read as zeros)"
+                  : "read_status: unknown device status " + std::to_string(value));
 }
 
 size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, int num_q_heads,
@@ -426,7 +615,8 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
                         void* out, void* workspace, size_t workspace_bytes, int batch, int total_q,
                         int64_t total_kv, int num_q_heads, int num_kv_heads, int head_dim,
                         int64_t num_slots, int dtype, float sm_scale, int max_len_extend,
-                        int is_cross_attention, int sliding_window_size, void* stream) {
+                        int is_cross_attention, int sliding_window_size, void* stream,
+                        const PageIndex* pages = nullptr) {
   const char* op = "paged_prefill_attention: ";
   if (total_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_slots < 0 || total_kv < 0)
     return fail(MSGL_BAD_SHAPE,
@@ -444,10 +634,21 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
   if (num_kv_heads > 65535)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "num_kv_heads must be <= 65535");
   if (max_len_extend < 1) max_len_extend = 1;
-  if (!q || !k_cache || !v_cache || !qo_indptr || !kv_indptr || !kv_indices || !prefix_lens || !out)
+  if (!q || !k_cache || !v_cache || !qo_indptr || !prefix_lens || !out ||
+      (!pages && (!kv_indptr || !kv_indices)))
     return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
   const int sms = sm_count_cached();
   if (sms <= 0) return fail(MSGL_CUDA_ERROR, std::string(op) + "cannot query the device");
+  CUtensorMap tm_k, tm_v;
+  std::memset(&tm_k, 0, sizeof(tm_k));
+  std::memset(&tm_v, 0, sizeof(tm_v));
+  if (pages && (!make_pool_tensor_map(&tm_k, k_cache, num_slots, num_kv_heads, head_dim, dtype) ||
+                !make_pool_tensor_map(&tm_v, v_cache, num_slots, num_kv_heads, head_dim, dtype)))
+    return fail(MSGL_CUDA_ERROR, std::string(op) + "cannot build the tensor maps of the K/V pool");
+  CUtensorMap tm_q;
+  std::memset(&tm_q, 0, sizeof(tm_q));
+  const bool q_tma = pages && make_query_tensor_map(&tm_q, q, total_q, num_q_heads,
+                                                    num_q_heads / num_kv_heads, head_dim, dtype);
   const PrefillPlan pl = plan_prefill(batch, total_q, total_kv, num_q_heads, num_kv_heads,
                                       head_dim, max_len_extend, sliding_window_size, sms);
   const size_t need = kStatusBytes + pl.plan_bytes + pl.part_ml_bytes + pl.part_o_bytes;
@@ -464,12 +665,19 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
   p.kv_indptr = kv_indptr;
   p.kv_indices = kv_indices;
   p.prefix_lens = prefix_lens;
+  if (pages) {
+    p.page_indptr = pages->page_indptr;
+    p.page_indices = pages->page_indices;
+    p.kv_lens = pages->kv_lens;
+    p.page_size = pages->page_size;
+  }
+  p.q_tma = q_tma ? 1 : 0;
   p.out = out;
   p.gate = gate;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   p.status = reinterpret_cast<int*>(ws);
   if (pl.kv_chunk > 0) {
-    p.plan = reinterpret_cast<int*>(ws + kStatusBytes);
+    p.tickets = reinterpret_cast<int*>(ws + 256);   // at most kPrefillTickets units when split
     p.part_ml = reinterpret_cast<float*>(ws + kStatusBytes + pl.plan_bytes);
     p.part_o = reinterpret_cast<float*>(ws + kStatusBytes + pl.plan_bytes + pl.part_ml_bytes);
   }
@@ -486,38 +694,33 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   dim3 grid(static_cast<unsigned>(pl.items * num_kv_heads));
-  dim3 mgrid(total_q, num_q_heads);
   const bool short_q = prefill_short_q(max_len_extend, p.group, head_dim);
   cudaError_t e;
-  auto launch = [&](auto kernel, auto merge, int threads, int smem) -> cudaError_t {
+  auto launch = [&](auto kernel, int threads, int smem) -> cudaError_t {
     cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, threads, smem, s>>>(p);
-    if (pl.kv_chunk > 0) return launch_dependent(merge, mgrid, dim3(head_dim), s, p);
+    kernel<<<grid, threads, smem, s>>>(p, tm_k, tm_v, tm_q);
     return cudaSuccess;
   };
-  using S1 = msgl::TcShape<1>;
-  using S2 = msgl::TcShape<2>;
-  using S1w = msgl::TcShape<1, 256>;
-  if (head_dim == 256) {
-    e = dtype == MSGL_DTYPE_BF16
-            ? launch(msgl::prefill_tc_kernel<__nv_bfloat16, 64, 1, 256>,
-                     msgl::prefill_merge_kernel<__nv_bfloat16, 256, S1w::kBM>, S1w::kThreads, S1w::kSmemBytes)
-            : launch(msgl::prefill_tc_kernel<__half, 64, 1, 256>,
-                     msgl::prefill_merge_kernel<__half, 256, S1w::kBM>, S1w::kThreads, S1w::kSmemBytes);
-  } else if (dtype == MSGL_DTYPE_BF16) {
-    using T = __nv_bfloat16;
-    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64, 1>, msgl::prefill_merge_kernel<T, 128, S1::kBM>,
-                         S1::kThreads, S1::kSmemBytes)
-                : launch(msgl::prefill_tc_kernel<T, 128, 2>, msgl::prefill_merge_kernel<T, 128, S2::kBM>,
-                         S2::kThreads, S2::kSmemBytes);
-  } else {
-    using T = __half;
-    e = short_q ? launch(msgl::prefill_tc_kernel<T, 64, 1>, msgl::prefill_merge_kernel<T, 128, S1::kBM>,
-                         S1::kThreads, S1::kSmemBytes)
-                : launch(msgl::prefill_tc_kernel<T, 128, 2>, msgl::prefill_merge_kernel<T, 128, S2::kBM>,
-                         S2::kThreads, S2::kSmemBytes);
-  }
+  // per element type: head_dim 256 / short query blocks / long chunks, each per-token or paged
+  auto dispatch = [&](auto tag) -> cudaError_t {
+    using T = decltype(tag);
+    using S1 = msgl::TcShape<1>;
+    using S2 = msgl::TcShape<2>;
+    using S1w = msgl::TcShape<1, 256>;
+    using P1 = msgl::TcShape<1, 128, true>;
+    using P2 = msgl::TcShape<2, 128, true>;
+    using P1w = msgl::TcShape<1, 256, true>;
+    if (head_dim == 256)
+      return pages ? launch(msgl::prefill_tc_kernel<T, 64, 1, 256, true>, P1w::kThreads, P1w::kSmemBytes)
+                   : launch(msgl::prefill_tc_kernel<T, 64, 1, 256>, S1w::kThreads, S1w::kSmemBytes);
+    if (short_q)
+      return pages ? launch(msgl::prefill_tc_kernel<T, 64, 1, 128, true>, P1::kThreads, P1::kSmemBytes)
+                   : launch(msgl::prefill_tc_kernel<T, 64, 1>, S1::kThreads, S1::kSmemBytes);
+    return pages ? launch(msgl::prefill_tc_kernel<T, 128, 2, 128, true>, P2::kThreads, P2::kSmemBytes)
+                 : launch(msgl::prefill_tc_kernel<T, 128, 2>, S2::kThreads, S2::kSmemBytes);
+  };
+  e = dtype == MSGL_DTYPE_BF16 ? dispatch(__nv_bfloat16{}) : dispatch(__half{});
   if (e != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail("paged_prefill_attention", e);
   return MSGL_OK;
@@ -556,7 +759,7 @@ int msgl_paged_prefill_attention_gated(const void* q, const void* k_cache, const
 int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, const void* k,
                         const void* v, int length, int num_kv_heads, int head_dim,
                         int64_t num_slots, int64_t cache_row_stride, int64_t input_row_stride,
-                        int dtype, void* stream) {
+                        int dtype, void* status_word, void* stream) {
   const char* op = "store_kv_cache: ";
   if (length < 0 || num_kv_heads <= 0 || head_dim <= 0 || num_slots < 0)
     return fail(MSGL_BAD_SHAPE,
@@ -593,12 +796,12 @@ int msgl_store_kv_cache(void* k_cache, void* v_cache, const int32_t* indices, co
     store_kv_kernel<16><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
         static_cast<unsigned char*>(k_cache), static_cast<unsigned char*>(v_cache), indices,
         static_cast<const unsigned char*>(k), static_cast<const unsigned char*>(v), length,
-        vec_per_row, crb, irb, num_slots, nullptr);
+        vec_per_row, crb, irb, num_slots, static_cast<int*>(status_word));
   else
     store_kv_kernel<8><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
         static_cast<unsigned char*>(k_cache), static_cast<unsigned char*>(v_cache), indices,
         static_cast<const unsigned char*>(k), static_cast<const unsigned char*>(v), length,
-        vec_per_row, crb, irb, num_slots, nullptr);
+        vec_per_row, crb, irb, num_slots, static_cast<int*>(status_word));
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("store_kv_cache", e);
   return MSGL_OK;
@@ -694,8 +897,8 @@ size_t msgl_page_index_workspace_bytes(int batch, int64_t total_pages, int page_
 // Builds kv_indptr and per-token kv_indices in `index_ws`; *total_kv_bound = total_pages * page_size.
 static int expand_page_index(const char* op_name, const int32_t* page_indptr,
                              const int32_t* page_indices, const int32_t* kv_lens, int batch,
-                             int64_t total_pages, int page_size, void* index_ws, int* status,
-                             const int32_t** kv_indptr, const int32_t** kv_indices,
+                             int64_t total_pages, int page_size, int64_t num_slots, void* index_ws,
+                             int* status, const int32_t** kv_indptr, const int32_t** kv_indices,
                              int64_t* total_kv_bound, void* stream) {
   const std::string op = std::string(op_name) + ": ";
   if (batch < 0 || total_pages < 0) return fail(MSGL_BAD_SHAPE, op + "negative size");
@@ -718,7 +921,8 @@ static int expand_page_index(const char* op_name, const int32_t* page_indptr,
     int bx = static_cast<int>((avg + 255) / 256);
     if (bx > 64) bx = 64;
     expand_page_indices_kernel<<<dim3(bx, batch), 256, 0, s>>>(page_indptr, page_indices, indptr,
-                                                                page_size, indices);
+                                                                page_size, total_pages, num_slots,
+                                                                indices, status);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(op_name, e);
@@ -742,10 +946,22 @@ int msgl_paged_decode_attention_p16(const void* q, const void* k_cache, const vo
     return fail(MSGL_BAD_ARG, std::string(op) + ": workspace too small: need " +
                                   std::to_string(op_ws + idx_ws) + " bytes, got " +
                                   std::to_string(workspace_bytes));
+  if (page_size % msgl::kTmaBoxRows == 0 && tensor_map_encoder() != nullptr) {
+    // Fast path: a warp's 16-token group is one TMA box copy per K/V half straight from the
+    // page id; no per-token index is built.
+    if (batch > 0 && (!page_indptr || !kv_lens || (total_pages > 0 && !page_indices)))
+      return fail(MSGL_BAD_ARG, std::string(op) + ": null tensor pointer");
+    if (total_pages * page_size >= (1ll << 31))
+      return fail(MSGL_BAD_SHAPE, std::string(op) + ": total_pages * page_size must be < 2^31");
+    const PageIndex pages{page_indptr, page_indices, kv_lens, page_size};
+    return decode_impl(q, k_cache, v_cache, nullptr, nullptr, num_kv_splits, nullptr, out, workspace,
+                       op_ws, batch, num_q_heads, num_kv_heads, head_dim, num_slots, dtype, sm_scale,
+                       max_kv_splits, stream, &pages);
+  }
   const int32_t *kv_indptr = nullptr, *kv_indices = nullptr;
   int64_t bound = 0;
   int rc = expand_page_index(op, page_indptr, page_indices, kv_lens, batch, total_pages, page_size,
-                             static_cast<unsigned char*>(workspace) + op_ws,
+                             num_slots, static_cast<unsigned char*>(workspace) + op_ws,
                              static_cast<int*>(workspace), &kv_indptr, &kv_indices, &bound, stream);
   if (rc != MSGL_OK) return rc;
   return decode_impl(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, nullptr, out, workspace,
@@ -785,10 +1001,24 @@ int msgl_paged_prefill_attention_p16(const void* q, const void* k_cache, const v
                                   std::to_string(total) + " bytes, got " +
                                   std::to_string(workspace_bytes));
   const size_t op_ws = total - idx_ws;
+  if (page_size % msgl::kTmaBoxRows == 0 && tensor_map_encoder() != nullptr) {
+    // Fast path: the 16 token rows of a page (or of a 16-row slice of a larger page) are
+    // contiguous in the pool, so the kernel copies them as TMA boxes straight from the page
+    // ids; no per-token index is built.
+    if (batch > 0 && (!page_indptr || !kv_lens || (total_pages > 0 && !page_indices)))
+      return fail(MSGL_BAD_ARG, std::string(op) + ": null tensor pointer");
+    if (total_pages * page_size >= (1ll << 31))
+      return fail(MSGL_BAD_SHAPE, std::string(op) + ": total_pages * page_size must be < 2^31");
+    const PageIndex pages{page_indptr, page_indices, kv_lens, page_size};
+    return prefill_impl(q, k_cache, v_cache, qo_indptr, nullptr, nullptr, prefix_lens, nullptr, out,
+                        workspace, op_ws, batch, total_q, total_pages * page_size, num_q_heads,
+                        num_kv_heads, head_dim, num_slots, dtype, sm_scale, max_len_extend,
+                        is_cross_attention, sliding_window_size, stream, &pages);
+  }
   const int32_t *kv_indptr = nullptr, *kv_indices = nullptr;
   int64_t bound = 0;
   int rc = expand_page_index(op, page_indptr, page_indices, kv_lens, batch, total_pages, page_size,
-                             static_cast<unsigned char*>(workspace) + op_ws,
+                             num_slots, static_cast<unsigned char*>(workspace) + op_ws,
                              static_cast<int*>(workspace), &kv_indptr, &kv_indices, &bound, stream);
   if (rc != MSGL_OK) return rc;
   return prefill_impl(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens, nullptr, out,
@@ -796,6 +1026,15 @@ int msgl_paged_prefill_attention_p16(const void* q, const void* k_cache, const v
                       num_slots, dtype, sm_scale, max_len_extend, is_cross_attention,
                       sliding_window_size, stream);
 }
+
+#ifdef MSGL_TRACE
+// Development builds only: copies the per-CTA trace of the last prefill launch to host memory.
+int msgl_debug_read_cta_trace(void* dst, int n_ctas) {
+  if (n_ctas > msgl::kTraceCtas) n_ctas = msgl::kTraceCtas;
+  cudaError_t e = cudaMemcpyFromSymbol(dst, msgl::g_cta_trace, sizeof(long long) * 32 * n_ctas);
+  return e == cudaSuccess ? MSGL_OK : cuda_fail("debug_read_cta_trace", e);
+}
+#endif
 
 int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64_t len_b,
                               int elem_bytes) {
@@ -824,9 +1063,10 @@ int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64
 
 int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
                            const int32_t* table_idx, const int32_t* kv_indptr,
-                           int32_t* kv_indices, int batch, int64_t total_kv, void* stream) {
+                           int32_t* kv_indices, int batch, int64_t total_kv, int64_t table_rows,
+                           int64_t table_cols, void* status_word, void* stream) {
   const char* op = "gather_kv_indices: ";
-  if (batch < 0 || total_kv < 0 || table_row_stride < 0)
+  if (batch < 0 || total_kv < 0 || table_row_stride < 0 || table_rows < 0 || table_cols < 0)
     return fail(MSGL_BAD_SHAPE, std::string(op) + "negative size");
   if (batch == 0 || total_kv == 0) return MSGL_OK;
   if (batch > 65535) return fail(MSGL_BAD_SHAPE, std::string(op) + "batch must be <= 65535");
@@ -837,7 +1077,8 @@ int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
   if (bx > 64) bx = 64;
   dim3 grid(bx, batch);
   gather_kv_indices_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      page_table, table_row_stride, table_idx, kv_indptr, kv_indices, batch);
+      page_table, table_row_stride, table_idx, kv_indptr, kv_indices, batch, table_rows, table_cols,
+      total_kv, static_cast<int*>(status_word));
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("gather_kv_indices", e);
   return MSGL_OK;

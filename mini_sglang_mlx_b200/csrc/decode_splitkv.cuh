@@ -11,8 +11,15 @@
 // row reductions are warp shuffles.  The warps' (max, sum, O) triples are
 // merged through shared memory; the CTA writes a normalised fp32 partial and
 // its log-sum-exp, or the final bf16/f16 row when the sequence has one split.
-// Pass 2 (decode_merge_kernel): one CTA per (q_head, sequence) merges the
-// partials by log-sum-exp.
+// Merge: the CTA of a (sequence, KV head) that finishes last (an arrival counter per pair)
+// combines the splits' partials by log-sum-exp and writes the final rows; there is no second
+// launch.
+//
+// Page-granular form (PAGED): a warp's 16-token group is one page (or a 16-row slice of a
+// larger page), contiguous in the pool, so lane 0 fetches its K and V rows with TMA box copies
+// (cp.async.bulk.tensor.2d, 16 rows x 64 elements, 128-byte swizzle) straight from the page id
+// and the warp waits on the stage's mbarrier; only a sequence's ragged last page is copied row
+// by row (rows past the length are zero-filled).
 //
 // Semantics follow the reference stages
 // (mini-sglang-mlx-kernel/csrc/paged_decode_attention.metal:313-506 and
@@ -32,10 +39,18 @@ struct DecodeParams {
   const int32_t* kv_indptr;
   const int32_t* kv_indices;
   const int32_t* num_kv_splits;  // may be null
+  // page-granular addressing (kv_lens != null): see PrefillParams
+  const int32_t* page_indptr;
+  const int32_t* page_indices;
+  const int32_t* kv_lens;
+  int page_size;
   void* out;
   const void* gate;  // (batch, hq, D) or null: out *= sigmoid(gate)
   float* part_o;    // (batch, hq, max_splits, D)
   float* part_lse;  // (batch, hq, max_splits)
+  // (batch, hkv) arrival counters of the splits of a (sequence, KV head): the CTA that arrives
+  // last merges the partials and puts the counter back to zero.  Zero before the first launch.
+  int* tickets;
   int* status;      // device status word (0 = ok); may be null
   int batch, hq, hkv, group;
   int max_splits;
@@ -55,9 +70,20 @@ __device__ __forceinline__ int decode_effective_splits(int L, const int32_t* hin
   return max(s, 1);
 }
 
-template <typename T, int HD, int NWARPS, int NSTAGES>
+// Length in tokens of sequence b (page-granular: clamped to the tokens its pages hold).
+__device__ __forceinline__ int decode_seq_len(const DecodeParams& p, int b) {
+  if (p.kv_lens) {
+    const int64_t cap =
+        static_cast<int64_t>(max(p.page_indptr[b + 1] - p.page_indptr[b], 0)) * p.page_size;
+    return static_cast<int>(min(static_cast<int64_t>(max(p.kv_lens[b], 0)), cap));
+  }
+  return p.kv_indptr[b + 1] - p.kv_indptr[b];
+}
+
+template <typename T, int HD, int NWARPS, int NSTAGES, bool PAGED = false>
 __global__ void __launch_bounds__(NWARPS * 32)
-    decode_partial_kernel(const DecodeParams p) {
+    decode_partial_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
+                          const __grid_constant__ CUtensorMap tm_v) {
   constexpr int CH = HD / 8;                              // 16-byte chunks per token row
   constexpr int ROW_BYTES = HD * 2;
   constexpr int TILE_BYTES = kDecodeGroupTokens * ROW_BYTES;  // one K (or V) group tile
@@ -74,8 +100,12 @@ __global__ void __launch_bounds__(NWARPS * 32)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int kv_begin = p.kv_indptr[b];
-  const int L = p.kv_indptr[b + 1] - kv_begin;
+  const int kv_begin = PAGED ? p.page_indptr[b] : p.kv_indptr[b];   // pages / tokens
+  const int L = decode_seq_len(p, b);
+  if (PAGED && split == 0 && h == 0 && threadIdx.x == 0 && p.status) {
+    const int len = p.kv_lens[b];   // negative or beyond the sequence's pages: clamped, reported
+    if (len < 0 || len > L) atomicExch(p.status, 2);
+  }
   const int splits = decode_effective_splits(L, p.num_kv_splits, b, p.max_splits, CTA_TOKENS);
   if (split >= splits) return;
   const int per = ceil_div(ceil_div(L, splits), CTA_TOKENS) * CTA_TOKENS;
@@ -110,7 +140,29 @@ __global__ void __launch_bounds__(NWARPS * 32)
   }
 
   // ---- warp-private ring of K/V group tiles
-  const uint32_t ring = smem_u32(smem_raw) + warp * (NSTAGES * 2 * TILE_BYTES);
+  // PAGED: tiles are TMA destinations with the 128-byte swizzle, which is a function of the
+  // shared-memory address: the ring starts on a 1024-byte boundary.  A tile is HD/64 column
+  // blocks of 16 rows x 128 bytes.
+  const uint32_t smem_pad = PAGED ? ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u) : 0u;
+  unsigned char* smem_al = smem_raw + smem_pad;
+  const uint32_t ring = smem_u32(smem_al) + warp * (NSTAGES * 2 * TILE_BYTES);
+  auto toff = [](int row, int chunk) -> uint32_t {
+    if constexpr (PAGED)
+      return static_cast<uint32_t>((chunk >> 3) * (kDecodeGroupTokens * 128) + (row << 7) +
+                                   (((chunk & 7) ^ (row & 7)) << 4));
+    else
+      return swz_offset<CH>(row, chunk);
+  };
+  __shared__ uint64_t s_bar[PAGED ? NWARPS * NSTAGES : 1];
+  if constexpr (PAGED) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < NWARPS * NSTAGES; ++i) mbar_init(smem_u32(&s_bar[i]), 1);
+      fence_mbar_init();
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
+    }
+    __syncthreads();
+  }
 
   // group g of this warp covers tokens [t_begin + (g*NWARPS + warp)*16, +16)
   const int first = t_begin + warp * kDecodeGroupTokens;
@@ -155,20 +207,101 @@ __global__ void __launch_bounds__(NWARPS * 32)
   for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-  // prologue: NSTAGES-1 groups in flight
-  int next_slot = load_idx(0);
+  // ---- PAGED: page of a step -> first pool row y and number of valid rows n (all lanes agree)
+  const int32_t* __restrict__ pages = PAGED ? p.page_indices + kv_begin : nullptr;
+  auto load_page = [&](int step, int& y, int& n) {
+    y = 0;
+    n = 0;
+    if (step < nsteps) {
+      const int t = first + step * CTA_TOKENS;
+      const int pg = __ldg(pages + t / p.page_size);
+      const int64_t row0 = static_cast<int64_t>(pg) * p.page_size + t % p.page_size;
+      const int nv = min(kDecodeGroupTokens, L - t);
+      if (pg < 0 || row0 + nv > p.num_slots) {
+        if (p.status && lane == 0) atomicExch(p.status, 2);   // page outside the pool: zeros
+      } else {
+        y = static_cast<int>(row0);
+        n = nv;
+      }
+    }
+  };
+  auto bar_of = [&](int stage) { return smem_u32(&s_bar[warp * NSTAGES + stage]); };
+  auto issue_page = [&](int stage, int y, int n) {
+    const uint32_t kdst = ring + stage * (2 * TILE_BYTES);
+    const uint32_t vdst = kdst + TILE_BYTES;
+    const uint32_t bar = bar_of(stage);
+    if (n == kDecodeGroupTokens) {
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar, 2 * TILE_BYTES);
 #pragma unroll
-  for (int s = 0; s < NSTAGES - 1; ++s) {
-    if (s < nsteps) issue(s, next_slot);
-    cp_async_commit();
-    next_slot = load_idx(s + 1);
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_2d(kdst + c * (kDecodeGroupTokens * 128), &tm_k, h * HD + c * 64, y, bar);
+          tma_load_2d(vdst + c * (kDecodeGroupTokens * 128), &tm_v, h * HD + c * 64, y, bar);
+        }
+      }
+    } else {
+      // ragged last page of the sequence (or a page outside the pool): valid rows by 16-byte
+      // copies, the rest zeros; waited for on the spot (once per sequence and KV head)
+#pragma unroll
+      for (int k = 0; k < kDecodeGroupTokens * CH / 32; ++k) {
+        const int e = k * 32 + lane;
+        const int row = e / CH, chunk = e % CH;
+        const bool ok = row < n;
+        const int64_t off =
+            (ok ? static_cast<int64_t>(y + row) * slot_stride + head_off : 0) + chunk * 16;
+        cp_async_16(kdst + toff(row, chunk), kbase + off, ok ? 16 : 0);
+        cp_async_16(vdst + toff(row, chunk), vbase + off, ok ? 16 : 0);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+    }
+  };
+
+  // prologue: NSTAGES-1 groups in flight
+  int next_slot = 0, next_y = 0, next_n = 0;
+  if constexpr (PAGED) {
+    int py[NSTAGES], pn[NSTAGES];
+#pragma unroll
+    for (int s = 0; s < NSTAGES; ++s) load_page(s, py[s], pn[s]);   // independent loads, in flight together
+#pragma unroll
+    for (int s = 0; s < NSTAGES - 1; ++s)
+      if (s < nsteps) issue_page(s, py[s], pn[s]);
+    next_y = py[NSTAGES - 1];
+    next_n = pn[NSTAGES - 1];
+  } else {
+    next_slot = load_idx(0);
+#pragma unroll
+    for (int s = 0; s < NSTAGES - 1; ++s) {
+      if (s < nsteps) issue(s, next_slot);
+      cp_async_commit();
+      next_slot = load_idx(s + 1);
+    }
   }
 
+  bool alive = true;
   for (int step = 0; step < nsteps; ++step) {
-    cp_async_wait<NSTAGES - 2>();
-    __syncwarp();
-    // refill the stage consumed in the previous iteration
-    {
+    if constexpr (PAGED) {
+      // bounded wait for this step's stage
+      const uint32_t bar = bar_of(step % NSTAGES);
+      const uint32_t parity = (step / NSTAGES) & 1;
+      bool ok = mbar_try_wait(bar, parity);
+      if (!ok) {
+        const long long t0 = clock64();
+        while (!(ok = mbar_try_wait(bar, parity)) && clock64() - t0 < kTcWaitCycles) {
+        }
+      }
+      alive = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+      if (!alive) break;
+      // refill the stage consumed in the previous iteration
+      const int nstep = step + NSTAGES - 1;
+      if (nstep < nsteps) issue_page(nstep % NSTAGES, next_y, next_n);
+      load_page(nstep + 1, next_y, next_n);
+    } else {
+      cp_async_wait<NSTAGES - 2>();
+      __syncwarp();
+      // refill the stage consumed in the previous iteration
       const int nstep = step + NSTAGES - 1;
       if (nstep < nsteps) issue(nstep % NSTAGES, next_slot);
       cp_async_commit();
@@ -188,7 +321,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
         uint32_t kf[4];
-        ldmatrix_x4(kf, kt + swz_offset<CH>(row, 2 * ks + (mat & 1)));
+        ldmatrix_x4(kf, kt + toff(row, 2 * ks + (mat & 1)));
         MmaOp<T>::run(s[0], qf[ks], kf[0], kf[1]);
         MmaOp<T>::run(s[1], qf[ks], kf[2], kf[3]);
       }
@@ -240,19 +373,20 @@ __global__ void __launch_bounds__(NWARPS * 32)
 #pragma unroll
       for (int j = 0; j < NT / 2; ++j) {
         uint32_t vf[4];
-        ldmatrix_x4_trans(vf, vt + swz_offset<CH>(row, 2 * j + (mat >> 1)));
+        ldmatrix_x4_trans(vf, vt + toff(row, 2 * j + (mat >> 1)));
         MmaOp<T>::run(o[2 * j], pa, vf[0], vf[1]);
         MmaOp<T>::run(o[2 * j + 1], pa, vf[2], vf[3]);
       }
     }
   }
   cp_async_wait<0>();
+  if (PAGED && !alive && p.status && lane == 0) atomicExch(p.status, 1);   // a wait ran out
   l0 = quad_sum(l0);
   l1 = quad_sum(l1);
   __syncthreads();  // every warp is done with its ring: reuse it for the merge
 
   // ---- merge the warps' partials
-  float* sm_m = reinterpret_cast<float*>(smem_raw);          // [NWARPS][16]
+  float* sm_m = reinterpret_cast<float*>(smem_al);           // [NWARPS][16]
   float* sm_l = sm_m + NWARPS * 16;                          // [NWARPS][16]
   float* sm_o = sm_l + NWARPS * 16;                          // [NWARPS][16][HD]
   {
@@ -305,33 +439,42 @@ __global__ void __launch_bounds__(NWARPS * 32)
           den > 0.f ? M * kLn2 + __logf(den) : -INFINITY;
     }
   }
-}
+  if (splits == 1) return;
 
-template <typename T, int HD, int CTA_TOKENS>
-__global__ void __launch_bounds__(HD) decode_merge_kernel(const DecodeParams p) {
-  const int hq = blockIdx.x;
-  const int b = blockIdx.y;
-  const int L = p.kv_indptr[b + 1] - p.kv_indptr[b];
-  const int splits = decode_effective_splits(L, p.num_kv_splits, b, p.max_splits, CTA_TOKENS);
-  if (splits <= 1) return;  // pass 1 already wrote the final row
-  grid_dependency_wait();   // the partials come from pass 1
-  const int64_t hq_idx = static_cast<int64_t>(b) * p.hq + hq;
-  const float* lse = p.part_lse + hq_idx * p.max_splits;
-  const float* po = p.part_o + hq_idx * p.max_splits * HD;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, lse[s]);
-  const int d = threadIdx.x;
-  float num = 0.f, den = 0.f;
-  if (M != -INFINITY) {
-    for (int s = 0; s < splits; ++s) {
-      const float w = __expf(lse[s] - M);
-      den += w;
-      num += w * po[s * HD + d];
+  // ---- the split that arrives last merges: out = sum_s e^(lse_s - M) O_s / sum_s e^(lse_s - M)
+  // (the second stage of the reference, paged_decode_attention.metal:512-586, without a launch)
+  __shared__ int s_last;
+  __threadfence();      // this thread's partials are visible device-wide before the arrival
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* ticket = p.tickets + static_cast<int64_t>(b) * p.hkv + h;
+    const int arrived = atomicAdd(ticket, 1);
+    s_last = (arrived == splits - 1) ? 1 : 0;
+    if (s_last) *ticket = 0;
+  }
+  __syncthreads();
+  if (s_last == 0) return;
+  __threadfence();
+  for (int g = 0; g < G; ++g) {
+    const int64_t hq_idx = static_cast<int64_t>(b) * p.hq + static_cast<int64_t>(h) * G + g;
+    const float* lse = p.part_lse + hq_idx * p.max_splits;
+    const float* po = p.part_o + hq_idx * p.max_splits * HD;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(lse + s));
+    for (int d = threadIdx.x; d < HD; d += NWARPS * 32) {
+      float num = 0.f, den = 0.f;
+      if (M != -INFINITY) {
+        for (int s = 0; s < splits; ++s) {
+          const float w = __expf(__ldcg(lse + s) - M);
+          den += w;
+          num += w * __ldcg(po + s * HD + d);
+        }
+      }
+      const float val = den > 0.f ? num / den : 0.f;
+      out[hq_idx * HD + d] = p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[hq_idx * HD + d])
+                                    : MmaOp<T>::from_float(val);
     }
   }
-  const float val = den > 0.f ? num / den : 0.f;
-  static_cast<T*>(p.out)[hq_idx * HD + d] =
-      p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[hq_idx * HD + d]) : MmaOp<T>::from_float(val);
 }
 
 }  // namespace msgl

@@ -36,6 +36,15 @@
 // at (r/8)*1024 + (r%8)*128 and its 16-byte chunk c at position c ^ (r%8).
 // This is the canonical 128-byte-swizzle layout, K-major for Q and K (rows =
 // M/N index) and MN-major for V (rows = K index).
+//
+// Page-granular form (PAGED): the pool is addressed by pages of 16 tokens (or a multiple), so
+// the 16 token rows of a page are contiguous in the pool and one TMA box copy
+// (cp.async.bulk.tensor.2d, 16 rows x 64 elements, 128-byte swizzle = exactly the tile layout
+// above) moves a quarter of a 64-key tile's K or V half.  One lane per page issues the copies
+// straight from the page ids, completion is counted in bytes on the tile's mbarrier; the seven
+// copying warps and the per-token id staging go away.  Only the ragged last page of a sequence
+// (and the pages of a tile past the sequence's end) are filled with 16-byte cp.async copies, so
+// that rows past the sequence's length are zeros rather than whatever the pool holds there.
 #pragma once
 
 #include <type_traits>
@@ -44,19 +53,46 @@
 
 namespace msgl {
 
+// Development aid, compiled in only with -DMSGL_TRACE: one record per CTA (SM, wall-clock entry
+// and exit, cycle counts at the milestones of softmax group 0) read back through
+// msgl_debug_read_cta_trace.
+#ifdef MSGL_TRACE
+constexpr int kTraceCtas = 8192;
+__device__ long long g_cta_trace[kTraceCtas][32];
+__device__ __forceinline__ long long trace_wall() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int trace_smid() {
+  int s;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(s));
+  return s;
+}
+#define MSGL_TR(slot, value)                                                   \
+  do {                                                                         \
+    if (blockIdx.x < kTraceCtas) g_cta_trace[blockIdx.x][slot] = (value);      \
+  } while (0)
+#else
+#define MSGL_TR(slot, value) do { } while (0)
+#endif
+
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
 
 // Shape of a CTA.  NSUB = 2: 256 query rows, 16 warps, all 512 TMEM columns, 160 KB K/V
 // ring, one CTA per SM.  NSUB = 1: 128 rows, 12 warps, 256 TMEM columns, 64 KB ring, two
 // CTAs per SM (short query blocks are bandwidth-bound: two independent pipelines per SM
 // keep more copies in flight).
-template <int NSUB, int HD = 128>
+//
+// PAGED: the softmax warps, the MMA warp and three producer warps (the first issues the TMA
+// copies, all three load Q): 4*NSUB + 4 warps.
+template <int NSUB, int HD = 128, bool PAGED = false>
 struct TcShape {
   static_assert(HD == 128 || (HD == 256 && NSUB == 1), "head_dim 256 runs the one-sub-tile shape");
   static constexpr int kBM = NSUB * kTcSub;                       // packed query rows per CTA
   static constexpr int kRowBytes = HD * 2;                        // one token row of one head
   static constexpr int kQTileBytes = kTcSub * kRowBytes;          // one 128-row query sub-tile
-  static constexpr int kWarps = NSUB == 2 ? 16 : 12;
+  static constexpr int kWarps = PAGED ? 4 * NSUB + 4 : (NSUB == 2 ? 16 : 12);
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kMmaWarp = 4 * NSUB;                       // after the softmax warps
   static constexpr int kProducerWarp0 = kMmaWarp + 1;             // ... the rest copy
@@ -67,55 +103,14 @@ struct TcShape {
   // register cap at launch: the one-sub-tile shapes start at 80 registers either way (the
   // setmaxnreg budgets below are written against that pool)
   static constexpr int kMinCtasForRegs = NSUB == 2 ? 1 : 2;
+  // The CTA's register pool is threads x registers at launch; setmaxnreg moves registers between
+  // the softmax warps and the others inside that pool.  The PAGED one-sub-tile shape (256 threads
+  // at 128 registers, two CTAs per SM = the whole register file) already gives its softmax warps
+  // what they need: no re-balancing there.
+  static constexpr bool kRebalanceRegs = !(PAGED && NSUB == 1);
 };
-constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
 
 // ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait: false after kTcWaitCycles or once another thread has given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag != 0 || clock64() - t0 > kTcWaitCycles) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-// Warp-uniform form: every lane waits, the warp agrees on the outcome, so that the
-// warp-collective instructions that follow are executed by all lanes or by none.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
-                                               volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
-}
-// Arrive on `bar` once all cp.async copies issued so far by this thread have landed.
-__device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void fence_mbar_init() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -294,14 +289,201 @@ struct TcBarriers {
   // (with one PV barrier a group that waits only now and then could not tell completion
   // j-2 from j by parity alone)
   uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];
+  // kv splits: stage[i] synchronises the 128 threads of softmax group i around the staging
+  // buffer of its partial; while the last arriver merges, msync synchronises all softmax
+  // threads and mload[b] counts the bytes of the bulk load into merge buffer b
+  uint64_t stage[2], msync, mload[6];
 };
 
-template <typename T, int BN, int NSUB, int HD = 128>
-__global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>::kMinCtasForRegs)
-    prefill_tc_kernel(const PrefillParams p) {
+// Merge of the kv-split partials of one (sequence, q tile, head) unit by the CTA that arrived
+// last, run by its NSW softmax warps, 64 rows at a time.  Every role of the CTA is done, so the
+// whole dynamic shared memory is free: buffer A takes split 0 and becomes the accumulator,
+// buffers B0 / B1 take the further splits in turn, each as one bulk load of a 64-row blob
+// (issued two splits ahead); their (m, l) pairs come by ordinary loads.  A warp owns RU rows at a
+// time and a lane 4 or 8 columns of a row; the last split is folded in and the rows are written
+// out in one go.
+// (The few fields of the launch parameters it needs come by value: taking the address of the
+// kernel's parameter block would make the kernel keep a local copy of it.)
+struct MergeArgs {
+  const float* part_o;
+  const float* part_ml;
+  void* out;
+  const void* gate;
+  int* status;
+  int hq, hkv, group;
+};
+template <typename T, int HD, int NSUB, int NSW, typename Shape>
+__device__ __noinline__ void merge_kv_splits(const MergeArgs p, TcBarriers& bars,
+                                             unsigned char* smem_raw, uint32_t smem0,
+                                             volatile int* abort_flag, int nsp, int64_t slot0,
+                                             int rows_valid, int pk0, int q_begin, int h) {
+  constexpr int BM = Shape::kBM;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.group;
+  __threadfence();
+  fence_proxy_async_all();
+  constexpr int RBF = HD * 4;
+  constexpr uint32_t kBlob = 64 * RBF;
+  constexpr int VPL = HD / 32;          // output columns per lane
+    constexpr int RU = 4;                 // rows a warp works on at a time (independent chains)
+  // (m, l) of the accumulator and of the two incoming splits: behind the three blobs where
+  // the shape has the room, else in static shared memory
+  // NB incoming buffers: as many as the shape's shared memory holds beside A, at most 5
+  constexpr int kRoom = NSUB * Shape::kQTileBytes + Shape::kRingBytes;
+  constexpr int NB = (kRoom - 4096) / static_cast<int>(kBlob) - 1 >= 5 ? 5 : 2;
+  constexpr bool kMlDynamic = (1 + NB) * kBlob + 4096 <= kRoom;
+  static_assert((1 + NB) * kBlob <= kRoom, "merge buffers");
+  __shared__ __align__(16) float s_ml_static[kMlDynamic ? 4 : 128 + 128 * NB];
+  const uint32_t buf_a = smem0;
+  unsigned char* gen_a = smem_raw + (smem0 - smem_u32(smem_raw));
+  float* ml_base = kMlDynamic ? reinterpret_cast<float*>(gen_a + (1 + NB) * kBlob) : s_ml_static;
+  float* s_m = ml_base;                                  // [64]
+  float* s_l = ml_base + 64;                             // [64]
+  float2* s_mlin = reinterpret_cast<float2*>(ml_base + 128);   // [NB][64]
+  const uint32_t bar_ms = smem_u32(&bars.msync);
+  uint32_t ms_phase = 0, ld_phase[1 + NB];
+#pragma unroll
+  for (int b3 = 0; b3 <= NB; ++b3) ld_phase[b3] = 0;
+  bool ok = true;
+  auto group_sync = [&]() {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_ms);
+    ok = mbar_wait_warp(bar_ms, ms_phase, abort_flag);
+    ms_phase ^= 1;
+  };
+  T* out = static_cast<T*>(p.out);
+  const T* gate = static_cast<const T*>(p.gate);
+  for (int half = 0; half * 64 < rows_valid && ok; ++half) {
+    const int hv = min(64, rows_valid - half * 64);
+    auto src_o = [&](int sp) {
+      return p.part_o + ((slot0 + static_cast<int64_t>(sp) * p.hkv) * BM + half * 64) * HD;
+    };
+    auto src_ml = [&](int sp) {
+      return p.part_ml + ((slot0 + static_cast<int64_t>(sp) * p.hkv) * BM + half * 64) * 2;
+    };
+    auto issue_load = [&](int sp, int b3) {   // b3: 0 = A, 1 + b = incoming buffer b
+      const uint32_t bar = smem_u32(&bars.mload[b3]);
+      mbar_arrive_expect_tx(bar, kBlob);
+      bulk_load(buf_a + b3 * kBlob, src_o(sp), kBlob, bar);
+    };
+    if (tid == 0) {
+      issue_load(0, 0);
+      for (int sp = 1; sp < nsp && sp <= NB; ++sp) issue_load(sp, sp);
+    }
+    if (tid < hv) {
+      float2 mls[1 + NB];
+#pragma unroll
+      for (int sp = 0; sp <= NB; ++sp)
+        mls[sp] = sp < nsp ? __ldcg(reinterpret_cast<const float2*>(src_ml(sp)) + tid) : make_float2(0.f, 0.f);
+      s_m[tid] = mls[0].x;
+      s_l[tid] = mls[0].y;
+#pragma unroll
+      for (int sp = 1; sp <= NB; ++sp) s_mlin[(sp - 1) * 64 + tid] = mls[sp];
+    }
+    ok = mbar_wait_warp(smem_u32(&bars.mload[0]), ld_phase[0], abort_flag);
+    ld_phase[0] ^= 1;
+    if (!ok) break;
+    for (int sp = 1; sp < nsp; ++sp) {
+      const int b = (sp - 1) % NB;
+      const bool final_split = sp == nsp - 1;   // fold it in and write the rows out in one go
+      ok = mbar_wait_warp(smem_u32(&bars.mload[1 + b]), ld_phase[1 + b], abort_flag);
+      ld_phase[1 + b] ^= 1;
+      if (!ok) break;
+      group_sync();                       // the (m, l) pairs of this split are in place
+      if (!ok) break;
+      const unsigned char* gen_b = gen_a + (1 + b) * kBlob;
+      for (int r0 = warp * RU; r0 < hv; r0 += NSW * RU) {
+        float a[RU], wgt[RU], mn[RU], ln[RU];
+#pragma unroll
+        for (int k = 0; k < RU; ++k) {
+          const int rr = min(r0 + k, hv - 1);
+          const float2 mls = s_mlin[b * 64 + rr];
+          const float mo = s_m[rr], lo = s_l[rr];
+          mn[k] = fmaxf(mo, mls.x);
+          a[k] = mo == -INFINITY ? 0.f : fast_exp2(mo - mn[k]);
+          wgt[k] = mls.x == -INFINITY ? 0.f : fast_exp2(mls.x - mn[k]);
+          ln[k] = lo * a[k] + wgt[k] * mls.y;
+        }
+        __syncwarp();                     // every lane has read (m, l) before lane 0 updates them
+        float4 acc[RU][VPL / 4];
+#pragma unroll
+        for (int k = 0; k < RU; ++k) {
+          const int rr = min(r0 + k, hv - 1);
+#pragma unroll
+          for (int e4 = 0; e4 < VPL / 4; ++e4) {
+            const int pos = ((lane * (VPL / 4) + e4) ^ (rr & 31)) << 4;
+            const float4 x = *reinterpret_cast<const float4*>(gen_b + rr * RBF + pos);
+            float4 y = *reinterpret_cast<const float4*>(gen_a + rr * RBF + pos);
+            y.x = y.x * a[k] + wgt[k] * x.x;
+            y.y = y.y * a[k] + wgt[k] * x.y;
+            y.z = y.z * a[k] + wgt[k] * x.z;
+            y.w = y.w * a[k] + wgt[k] * x.w;
+            acc[k][e4] = y;
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < RU; ++k) {
+          const int rr = r0 + k;
+          if (rr >= hv) break;
+          if (!final_split) {
+#pragma unroll
+            for (int e4 = 0; e4 < VPL / 4; ++e4) {
+              const int pos = ((lane * (VPL / 4) + e4) ^ (rr & 31)) << 4;
+              *reinterpret_cast<float4*>(gen_a + rr * RBF + pos) = acc[k][e4];
+            }
+            if (lane == 0) {
+              s_m[rr] = mn[k];
+              s_l[rr] = ln[k];
+            }
+          } else {
+            const float invd = ln[k] > 0.f ? 1.f / ln[k] : 0.f;
+            const int pkr = pk0 + half * 64 + rr;
+            const int tlr = pkr / G, gr = pkr - tlr * G;
+            const int64_t oi =
+                (static_cast<int64_t>(q_begin + tlr) * p.hq + static_cast<int64_t>(h) * G + gr) * HD +
+                lane * VPL;
+            alignas(16) T vals[VPL];
+#pragma unroll
+            for (int e4 = 0; e4 < VPL / 4; ++e4) {
+              const float f[4] = {acc[k][e4].x * invd, acc[k][e4].y * invd, acc[k][e4].z * invd,
+                                  acc[k][e4].w * invd};
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                vals[4 * e4 + e] =
+                    gate ? apply_gate<T>(f[e], gate[oi + 4 * e4 + e]) : MmaOp<T>::from_float(f[e]);
+            }
+            if constexpr (VPL == 4)
+              *reinterpret_cast<uint2*>(out + oi) = *reinterpret_cast<const uint2*>(vals);
+            else
+              *reinterpret_cast<uint4*>(out + oi) = *reinterpret_cast<const uint4*>(vals);
+          }
+        }
+      }
+      group_sync();                       // everyone is done with buffer b and its (m, l)
+      if (!ok) break;
+      if (sp + NB < nsp) {
+        if (tid == 0) {
+          fence_proxy_async_all();
+          issue_load(sp + NB, 1 + b);
+        }
+        if (tid < hv)
+          s_mlin[b * 64 + tid] = __ldcg(reinterpret_cast<const float2*>(src_ml(sp + NB)) + tid);
+      }
+    }
+    if (!ok) break;
+  }
+  if (!ok && p.status && tid == 0) atomicExch(p.status, 1);
+}
+
+template <typename T, int BN, int NSUB, int HD = 128, bool PAGED = false>
+__global__ void __launch_bounds__(TcShape<NSUB, HD, PAGED>::kThreads,
+                                  TcShape<NSUB, HD, PAGED>::kMinCtasForRegs)
+    prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_q) {
   static_assert(BN == 64 || BN == 128, "key tile of 64 or 128 tokens");
   static_assert(NSUB == 2 || BN == 64, "the one-sub-tile shape has TMEM for 64-column score tiles only");
-  using Shape = TcShape<NSUB, HD>;
+  using Shape = TcShape<NSUB, HD, PAGED>;
   constexpr int kTcQTileBytes = Shape::kQTileBytes;
   constexpr int CPR = HD / 8;                          // 16-byte chunks of a token row
   constexpr int BM = Shape::kBM, SUB = kTcSub;
@@ -324,18 +506,73 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int G = p.group;
+#ifdef MSGL_TRACE
+  if (tid == 0) {
+    MSGL_TR(0, trace_wall());
+    MSGL_TR(1, clock64());
+    MSGL_TR(2, trace_smid());
+  }
+#endif
+
+  // ---- barriers and tensor memory first: neither depends on which work item this CTA gets
+  const uint32_t bar_q = smem_u32(&bars.q_full);
+  auto bar_full = [&](int bf) { return smem_u32(&bars.full[bf]); };
+  auto bar_empty = [&](int bf) { return smem_u32(&bars.empty[bf]); };
+  auto bar_sf = [&](int i, int sb) { return smem_u32(&bars.s_full[i][sb]); };
+  auto bar_pf = [&](int i, int sb) { return smem_u32(&bars.p_full[i][sb]); };
+  auto bar_pv = [&](int i, int sb) { return smem_u32(&bars.pv_done[i][sb]); };
+  // Q arrives as TMA boxes when the caller could describe it (query heads per KV head a power
+  // of two), else as 16-byte copies by the producer threads
+  const bool q_tma = PAGED && p.q_tma != 0;
+
+  if (tid == 0) {
+    s_abort = 0;
+    mbar_init(bar_q, q_tma ? 1 : NPROD);
+    mbar_init(smem_u32(&bars.idx_sync), NPROD);
+    for (int bf = 0; bf < kTcBufs; ++bf) {
+      // PAGED: the 32 lanes of the copying warp (their cp.async arrivals) + the arrival that
+      // announces the TMA bytes
+      mbar_init(bar_full(bf), PAGED ? 33 : NPROD);
+      mbar_init(bar_empty(bf), 1);
+    }
+    mbar_init(smem_u32(&bars.msync), kMmaWarp);          // one arrival per softmax warp
+    for (int b3 = 0; b3 < 6; ++b3) mbar_init(smem_u32(&bars.mload[b3]), 1);
+    for (int i = 0; i < NSUB; ++i) {
+      mbar_init(smem_u32(&bars.stage[i]), SUB / 32);     // one arrival per warp of the group
+      mbar_init(bar_sf(i, 0), 1);
+      mbar_init(bar_sf(i, 1), 1);
+      mbar_init(bar_pf(i, 0), SUB / 32);
+      mbar_init(bar_pf(i, 1), SUB / 32);
+      mbar_init(bar_pv(i, 0), 1);
+      mbar_init(bar_pv(i, 1), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&s_tmem_base), Shape::kTmemCols);
+    tmem_relinquish();
+  }
 
   ItemCoord it;
-  if (!find_item<kTcThreads>(p, static_cast<int>(blockIdx.x), BM, reinterpret_cast<int*>(smem_raw), it))
-    return;  // block-uniform
+  const bool have_item =
+      find_item<kTcThreads>(p, static_cast<int>(blockIdx.x), BM, reinterpret_cast<int*>(smem_raw), it);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (!have_item) {  // block-uniform: a launch rank past the last item
+    if (warp == kMmaWarp) tmem_dealloc(s_tmem_base, Shape::kTmemCols);
+    return;
+  }
   const int h = it.h;
   const SeqShape sq = load_seq_shape(p, it.b, BM);
   const int qt = it.qt, split = it.split;
-  if (p.plan && it.first && tid == 0) {
-    p.plan[2 * it.b] = it.base;
-    p.plan[2 * it.b + 1] = sq.nsplit;
-  }
   const int slot_item = it.base + qt * sq.nsplit + split;   // where this item's kv-split partial goes
+  if (PAGED && it.first && tid == 0 && p.status) {
+    // a length that is negative or exceeds the sequence's pages was clamped: report it
+    const int64_t cap = static_cast<int64_t>(p.page_indptr[it.b + 1] - p.page_indptr[it.b]) * p.page_size;
+    const int len = p.kv_lens[it.b];
+    if (len < 0 || len > cap) atomicExch(p.status, 2);
+  }
 
   // ---- geometry of the CTA's rows and of each sub-tile
   const int pk0 = qt * BM;
@@ -366,45 +603,19 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
   const uint32_t q_smem = smem0;                                   // 2 sub-tiles
   const uint32_t ring = smem0 + NSUB * kTcQTileBytes;              // kTcBufs K/V tiles
 
-  const uint32_t bar_q = smem_u32(&bars.q_full);
-  auto bar_full = [&](int bf) { return smem_u32(&bars.full[bf]); };
-  auto bar_empty = [&](int bf) { return smem_u32(&bars.empty[bf]); };
-  auto bar_sf = [&](int i, int sb) { return smem_u32(&bars.s_full[i][sb]); };
-  auto bar_pf = [&](int i, int sb) { return smem_u32(&bars.p_full[i][sb]); };
-  auto bar_pv = [&](int i, int sb) { return smem_u32(&bars.pv_done[i][sb]); };
-
-  if (tid == 0) {
-    s_abort = 0;
-    mbar_init(bar_q, NPROD);
-    mbar_init(smem_u32(&bars.idx_sync), NPROD);
-    for (int bf = 0; bf < kTcBufs; ++bf) {
-      mbar_init(bar_full(bf), NPROD);
-      mbar_init(bar_empty(bf), 1);
-    }
-    for (int i = 0; i < NSUB; ++i) {
-      mbar_init(bar_sf(i, 0), 1);
-      mbar_init(bar_sf(i, 1), 1);
-      mbar_init(bar_pf(i, 0), SUB / 32);
-      mbar_init(bar_pf(i, 1), SUB / 32);
-      mbar_init(bar_pv(i, 0), 1);
-      mbar_init(bar_pv(i, 1), 1);
-    }
-    fence_mbar_init();
-  }
-  if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&s_tmem_base), Shape::kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tmem = s_tmem_base;
   volatile int* abort_flag = &s_abort;
+#ifdef MSGL_TRACE
+  if (tid == 0) {
+    MSGL_TR(3, clock64());          // set-up done
+    MSGL_TR(4, ntiles);
+  }
+#endif
 
   // Register budget: the softmax warps hold a whole score row per thread, the others need
   // little.  Each warpgroup executes one and the same setmaxnreg instruction.
   if (warp >= kMmaWarp) {
-  reg_dec<56>();
+  if constexpr (Shape::kRebalanceRegs) reg_dec<56>();
   if (warp >= kTcProducerWarp0) {
     // =========================================================== producers
     const int ptid = tid - kTcProducerWarp0 * 32;  // 0..NPROD-1
@@ -416,83 +627,204 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
     const int64_t slot_stride = static_cast<int64_t>(p.hkv) * (HD * 2);
     const int64_t head_off = static_cast<int64_t>(h) * (HD * 2);
 
-    // Q: rows_valid packed rows, the rest zero
-    for (int i = 0; i < (BM + PROWS - 1) / PROWS; ++i) {
-      const int row = i * PROWS + rsub;  // 0..255
-      if (row >= nsub * SUB) break;
-      const int pk = pk0 + row;
-      const int tl = pk / G, g = pk - tl * G;
-      const bool ok = row < rows_valid;
-      const int64_t off =
-          ok ? ((static_cast<int64_t>(sq.q_begin + tl) * p.hq + static_cast<int64_t>(h) * G + g) * HD)
-             : 0;
-      cp_async_16(q_smem + (row >> 7) * kTcQTileBytes + tc_tile_offset<128>(row & 127, chunk),
-                  reinterpret_cast<const unsigned char*>(q + off) + chunk * 16, ok ? 16 : 0);
-    }
-    cp_async_mbar_arrive(bar_q);
-
-    constexpr int RPT = (BN + PROWS - 1) / PROWS;  // passes over a tile
-    // Slot ids are staged in shared memory: thread r fetches the id of row r of a tile (one
-    // coalesced load per tile, two tiles ahead of its use), out-of-range ids are reported
-    // once and stored as -1 (row treated as absent).  Tile t lives in s_slots[(t % (LA+1)) * BN ..].
-    const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
-    auto fetch_slot = [&](int tile) -> int {
-      const int t = kv_lo + tile * BN + ptid;
-      return (ptid < BN && tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
-    };
-    auto stage_slot = [&](int tile, int slot) {
-      if (ptid < BN) {
-        if (slot < -1 || static_cast<int64_t>(slot) >= p.num_slots) {
-          if (p.status) atomicExch(p.status, 2);
-          slot = -1;
-        }
-        s_slots[(tile % (LA + 1)) * BN + ptid] = slot;
-      }
-    };
-    bool alive = true;
-    uint32_t idx_phase = 0;
-    const uint32_t bar_idx = smem_u32(&bars.idx_sync);
-    auto producers_sync = [&]() {  // bounded barrier among the 128 producer threads
-      mbar_arrive(bar_idx);
-      alive = mbar_wait_warp(bar_idx, idx_phase, abort_flag);
-      idx_phase ^= 1;
-    };
-    // copy one tile into the ring buffer of sequence number `seq`
-    auto produce = [&](int seq, const unsigned char* src_base, int tile) {
-      const int bf = seq % kTcBufs;
-      alive = mbar_wait_warp(bar_empty(bf), ((seq / kTcBufs) & 1) ^ 1, abort_flag);
-      if (!alive) return;
-      const uint32_t dst = ring + bf * kTcKvTileBytes;
-      const int* slots = s_slots + (tile % (LA + 1)) * BN;
+    if (q_tma) {
+      // Q: one box per sub-tile and 64-element column block.  The tensor map is
+      // (head_dim, query heads, tokens) with a box of 64 x G x 128/G, so the rows land in
+      // packed order (token-major, the G heads of this KV head inside a token).  Rows past the
+      // sequence's last query token hold a neighbour's rows (or zeros past the last token of
+      // the batch); they are computed on and never written out.
+      if (warp == kTcProducerWarp0 && lane == 0) {
+        prefetch_tensormap(&tm_q);
+        mbar_arrive_expect_tx(bar_q, nsub * kTcQTileBytes);
+        for (int i = 0; i < nsub; ++i)
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int row = i * PROWS + rsub;
-        if (BN % PROWS != 0 && row >= BN) break;
-        const int slot = slots[row];
-        const bool ok = slot >= 0;
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_3d(q_smem + i * kTcQTileBytes + c * (SUB * 128), &tm_q, c * 64, h * G,
+                        sq.q_begin + tok_first + i * (SUB / G), bar_q);
+      }
+    } else {
+      // Q: rows_valid packed rows, the rest zero
+      for (int i = 0; i < (BM + PROWS - 1) / PROWS; ++i) {
+        const int row = i * PROWS + rsub;  // 0..255
+        if (row >= nsub * SUB) break;
+        const int pk = pk0 + row;
+        const int tl = pk / G, g = pk - tl * G;
+        const bool ok = row < rows_valid;
         const int64_t off =
-            (ok ? static_cast<int64_t>(slot) * slot_stride + head_off : 0) + chunk * 16;
-        cp_async_16(dst + tc_tile_offset<BN>(row, chunk), src_base + off, ok ? 16 : 0);
+            ok ? ((static_cast<int64_t>(sq.q_begin + tl) * p.hq + static_cast<int64_t>(h) * G + g) * HD)
+               : 0;
+        cp_async_16(q_smem + (row >> 7) * kTcQTileBytes + tc_tile_offset<128>(row & 127, chunk),
+                    reinterpret_cast<const unsigned char*>(q + off) + chunk * 16, ok ? 16 : 0);
       }
-      cp_async_mbar_arrive(bar_full(bf));
-    };
+      cp_async_mbar_arrive(bar_q);
+    }
+
+    bool alive = true;
+    if constexpr (PAGED) {
+      // ------------------------------------------------ page-granular: TMA boxes from the page ids
+      if (warp == kTcProducerWarp0) {
+        constexpr int PPT = BN / kTmaBoxRows;            // boxes (= lanes at work) per tile
+        constexpr int NQ = HD / 64;                      // 128-byte column blocks of a token row
+        constexpr uint32_t kBoxBytes = kTmaBoxRows * 128;
+        const int32_t* __restrict__ pages = p.page_indices + sq.kv_begin;
+        const int x0 = h * HD;
+        if (lane == 0) {
+          prefetch_tensormap(&tm_k);
+          prefetch_tensormap(&tm_v);
+        }
+        // Lane i < PPT owns box i of a tile (tokens [16 i, 16 i + 16) of the tile): y = its first
+        // pool row, n = how many of its rows belong to the sequence (16: a TMA box; fewer: rows
+        // by cp.async, the rest zero-filled; 0: all zeros).
+        auto fetch_box = [&](int tile, int& y, int& n) {
+          y = 0;
+          n = 0;
+          const int t0 = kv_lo + tile * BN + lane * kTmaBoxRows;
+          if (lane < PPT && tile < ntiles && t0 < kv_hi_load) {
+            const int pg = __ldg(pages + t0 / p.page_size);
+            const int64_t row0 = static_cast<int64_t>(pg) * p.page_size + t0 % p.page_size;
+            const int nv = min(kTmaBoxRows, sq.L - t0);
+            if (pg < 0 || row0 + nv > p.num_slots) {
+              if (p.status) atomicExch(p.status, 2);   // page outside the pool: rows read as zeros
+            } else {
+              y = static_cast<int>(row0);
+              n = nv;
+            }
+          }
+        };
+        int issued_seq = -1;   // ring sequence number of the last tile whose copies were issued
+        auto produce = [&](int seq, const CUtensorMap* tm, const unsigned char* src_base, int y, int n) {
+          const int bf = seq % kTcBufs;
+          alive = mbar_wait_warp(bar_empty(bf), ((seq / kTcBufs) & 1) ^ 1, abort_flag);
+          if (!alive) return;
+          const uint32_t dst = ring + bf * kTcKvTileBytes;
+          const uint32_t bar = bar_full(bf);
+          const bool full = n == kTmaBoxRows;
+          const uint32_t full_mask = __ballot_sync(0xffffffffu, full);
+          if (lane == 0) mbar_arrive_expect_tx(bar, __popc(full_mask) * (kTmaBoxRows * HD * 2));
+          __syncwarp();
+          if (full) {
 #pragma unroll
-    for (int t = 0; t <= LA; ++t) stage_slot(t, fetch_slot(t));
-    producers_sync();
-    for (int t = 0; t < LA && t < ntiles && alive; ++t) produce(ring_seq_k<LA>(t), kbase, t);
+            for (int c = 0; c < NQ; ++c)
+              tma_load_2d(dst + c * (BN * 128) + lane * kBoxBytes, tm, x0 + c * 64, y, bar);
+          }
+          uint32_t rest = ~full_mask & ((1u << PPT) - 1u);
+          while (rest) {   // warp-uniform
+            const int i = __ffs(rest) - 1;
+            rest &= rest - 1;
+            const int yi = __shfl_sync(0xffffffffu, y, i), ni = __shfl_sync(0xffffffffu, n, i);
+#pragma unroll
+            for (int k = 0; k < kTmaBoxRows * CPR / 32; ++k) {
+              const int e = k * 32 + lane;
+              const int row = e / CPR, chunk = e % CPR;
+              const bool ok = row < ni;
+              const int64_t off =
+                  (ok ? static_cast<int64_t>(yi + row) * slot_stride + head_off : 0) + chunk * 16;
+              cp_async_16(dst + tc_tile_offset<BN>(i * kTmaBoxRows + row, chunk), src_base + off,
+                          ok ? 16 : 0);
+            }
+          }
+          cp_async_mbar_arrive(bar);
+          issued_seq = seq;
+        };
+        // window of the boxes of tiles j .. j+LA (tile j: V next, tile j+LA: K next)
+        int wy[LA + 1], wn[LA + 1];
+#pragma unroll
+        for (int t = 0; t <= LA; ++t) fetch_box(t, wy[t], wn[t]);
+#pragma unroll
+        for (int t = 0; t < LA; ++t)
+          if (t < ntiles && alive) produce(ring_seq_k<LA>(t), &tm_k, kbase, wy[t], wn[t]);
 #pragma unroll 1
-    for (int j = 0; j < ntiles && alive; ++j) {
-      const int next_slot = fetch_slot(j + LA + 1);  // in flight while this tile's copies are issued
-      produce(ring_seq_v<LA>(j), vbase, j);
-      if (!alive) break;
-      if (j + LA < ntiles) {
-        produce(ring_seq_k<LA>(j + LA), kbase, j + LA);
-        if (!alive) break;
+        for (int j = 0; j < ntiles && alive; ++j) {
+          int ny, nn;
+          fetch_box(j + LA + 1, ny, nn);   // in flight while this step's copies are issued
+          produce(ring_seq_v<LA>(j), &tm_v, vbase, wy[0], wn[0]);
+          if (!alive) break;
+          if (j + LA < ntiles) {
+            produce(ring_seq_k<LA>(j + LA), &tm_k, kbase, wy[LA], wn[LA]);
+            if (!alive) break;
+          }
+#pragma unroll
+          for (int t = 0; t < LA; ++t) {
+            wy[t] = wy[t + 1];
+            wn[t] = wn[t + 1];
+          }
+          wy[LA] = ny;
+          wn[LA] = nn;
+        }
+        if (!alive) {
+          // gave up: let the bulk copies still in flight (at most a ring's worth) land before the
+          // CTA's shared memory goes away; bounded
+          const long long t0 = clock64();
+          for (int sq_i = max(0, issued_seq - kTcBufs + 1); sq_i <= issued_seq; ++sq_i) {
+            while (!mbar_try_wait(bar_full(sq_i % kTcBufs), (sq_i / kTcBufs) & 1) &&
+                   clock64() - t0 < 2000000LL) {
+            }
+          }
+        }
       }
-      producers_sync();               // every producer is done reading tile j's ids
-      if (!alive) break;
-      stage_slot(j + LA + 1, next_slot);  // reuses tile j's place
+    } else {
+      constexpr int RPT = (BN + PROWS - 1) / PROWS;  // passes over a tile
+      // Slot ids are staged in shared memory: thread r fetches the id of row r of a tile (one
+      // coalesced load per tile, two tiles ahead of its use), out-of-range ids are reported
+      // once and stored as -1 (row treated as absent).  Tile t lives in s_slots[(t % (LA+1)) * BN ..].
+      const int32_t* __restrict__ idx = p.kv_indices + sq.kv_begin;
+      auto fetch_slot = [&](int tile) -> int {
+        const int t = kv_lo + tile * BN + ptid;
+        return (ptid < BN && tile < ntiles && t < kv_hi_load) ? __ldg(idx + t) : -1;
+      };
+      auto stage_slot = [&](int tile, int slot) {
+        if (ptid < BN) {
+          if (slot < -1 || static_cast<int64_t>(slot) >= p.num_slots) {
+            if (p.status) atomicExch(p.status, 2);
+            slot = -1;
+          }
+          s_slots[(tile % (LA + 1)) * BN + ptid] = slot;
+        }
+      };
+      uint32_t idx_phase = 0;
+      const uint32_t bar_idx = smem_u32(&bars.idx_sync);
+      auto producers_sync = [&]() {  // bounded barrier among the 128 producer threads
+        mbar_arrive(bar_idx);
+        alive = mbar_wait_warp(bar_idx, idx_phase, abort_flag);
+        idx_phase ^= 1;
+      };
+      // copy one tile into the ring buffer of sequence number `seq`
+      auto produce = [&](int seq, const unsigned char* src_base, int tile) {
+        const int bf = seq % kTcBufs;
+        alive = mbar_wait_warp(bar_empty(bf), ((seq / kTcBufs) & 1) ^ 1, abort_flag);
+        if (!alive) return;
+        const uint32_t dst = ring + bf * kTcKvTileBytes;
+        const int* slots = s_slots + (tile % (LA + 1)) * BN;
+  #pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const int row = i * PROWS + rsub;
+          if (BN % PROWS != 0 && row >= BN) break;
+          const int slot = slots[row];
+          const bool ok = slot >= 0;
+          const int64_t off =
+              (ok ? static_cast<int64_t>(slot) * slot_stride + head_off : 0) + chunk * 16;
+          cp_async_16(dst + tc_tile_offset<BN>(row, chunk), src_base + off, ok ? 16 : 0);
+        }
+        cp_async_mbar_arrive(bar_full(bf));
+      };
+  #pragma unroll
+      for (int t = 0; t <= LA; ++t) stage_slot(t, fetch_slot(t));
       producers_sync();
+      for (int t = 0; t < LA && t < ntiles && alive; ++t) produce(ring_seq_k<LA>(t), kbase, t);
+  #pragma unroll 1
+      for (int j = 0; j < ntiles && alive; ++j) {
+        const int next_slot = fetch_slot(j + LA + 1);  // in flight while this tile's copies are issued
+        produce(ring_seq_v<LA>(j), vbase, j);
+        if (!alive) break;
+        if (j + LA < ntiles) {
+          produce(ring_seq_k<LA>(j + LA), kbase, j + LA);
+          if (!alive) break;
+        }
+        producers_sync();               // every producer is done reading tile j's ids
+        if (!alive) break;
+        stage_slot(j + LA + 1, next_slot);  // reuses tile j's place
+        producers_sync();
+      }
     }
     cp_async_wait<0>();
     if (!alive && p.status && ptid == 0) atomicExch(p.status, 1);
@@ -595,7 +927,9 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
   }
   } else {
     // =========================================================== softmax groups
-    if (NSUB == 2) reg_inc<200>(); else reg_inc<128>();
+    if constexpr (Shape::kRebalanceRegs) {
+      if (NSUB == 2) reg_inc<200>(); else reg_inc<128>();
+    }
     const int i = warp >> 2;                 // sub-tile
     const int r = tid & 127;                 // row inside the sub-tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -620,6 +954,10 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
       alive = mbar_wait_warp(bar_sf(i, sb), (j / LA) & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
+#ifdef MSGL_TRACE
+      if (tid == 0 && j == 0) MSGL_TR(5, clock64());   // first scores ready
+      if (tid == 0 && j == 8) MSGL_TR(9, clock64());   // ninth
+#endif
       const int k0 = kv_lo + j * BN;
       const bool need_mask = !(k0 >= vlo && k0 + BN - 1 <= vhi);
       // ---- the score row of this tile into registers
@@ -711,6 +1049,9 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
       if (lane == 0) mbar_arrive(bar_pf(i, sb));
     }
 
+#ifdef MSGL_TRACE
+    if (tid == 0) MSGL_TR(6, clock64());               // last P handed over
+#endif
     // ---- epilogue
     if (alive && my_tiles > 0) {
       alive = mbar_wait_warp(bar_pv(i, (my_tiles - 1) % LA), ((my_tiles - 1) / LA) & 1, abort_flag);
@@ -718,7 +1059,7 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
     }
     if (alive) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      if (p.kv_chunk == 0) {
+      if (p.kv_chunk == 0 || sq.nsplit == 1) {
         // Each warp stages its 32 output rows (HD*2 bytes each) in the Q sub-tile's shared memory,
         // free once the last S MMA has completed, then writes them out as whole rows (two per
         // instruction at head_dim 128); chunk c of row r sits at chunk position c ^ (r & 15)
@@ -776,85 +1117,122 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD>::kThreads, TcShape<NSUB, HD>
           }
         }
       } else {
-        // unnormalised partial of this kv split (empty split: max = -inf, sum = 0)
+        // Unnormalised partial of this kv split (empty split: max = -inf, sum = 0).  (m, l) go
+        // straight to scratch; the fp32 rows of O are staged, 64 rows at a time, in the
+        // sub-tile's Q buffer (free: every S MMA of the sub-tile is done) and leave as ONE bulk
+        // copy per 64 rows.  In the staging buffer (and so in scratch) the 16-byte chunk c of
+        // row r sits at chunk position c ^ (r & 31): conflict-free for the row-per-thread
+        // writes here and for the row-per-warp reads of the merge.
         const int64_t slot = static_cast<int64_t>(slot_item) * p.hkv + h;
-        float* po = p.part_o + (slot * BM + row) * HD;
         if (valid) {
           *reinterpret_cast<float2*>(p.part_ml + (slot * BM + row) * 2) =
               make_float2(my_tiles > 0 ? m_ref : -INFINITY, my_tiles > 0 ? l : 0.f);
         }
+        constexpr int RBF = HD * 4;                       // bytes of an fp32 row
+        const uint32_t stage_u = q_smem + i * kTcQTileBytes;   // 64 rows x RBF = one Q sub-tile
+        unsigned char* stage = smem_raw + (stage_u - smem_u32(smem_raw));
+        const int rows_sub = rows_valid - i * SUB;        // valid rows of this sub-tile (group-uniform)
+        const uint32_t bar_st = smem_u32(&bars.stage[i]);
+        uint32_t st_phase = 0;
+        for (int hb = 0; hb < 2 && alive; ++hb) {
+          if (rows_sub <= hb * 64) break;
+          if ((r >> 6) == hb) {                           // warp-uniform
+            const int rr = r & 63;
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          if (my_tiles > 0) {
-            tmem_ld32(o_tm + c * 32, v);
-            tmem_wait_ld();
-            reg_fence(v);
-          } else {
+            for (int c = 0; c < HD / 32; ++c) {
+              uint32_t v[32];
+              if (my_tiles > 0) {
+                tmem_ld32(o_tm + c * 32, v);
+                tmem_wait_ld();
+                reg_fence(v);
+              } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0u;
-          }
-          if (valid) {
+                for (int e = 0; e < 32; ++e) v[e] = 0u;
+              }
 #pragma unroll
-            for (int e = 0; e < 32; e += 4)
-              *reinterpret_cast<uint4*>(po + c * 32 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+              for (int e = 0; e < 32; e += 4) {
+                const int chunk = c * 8 + (e >> 2);
+                *reinterpret_cast<uint4*>(stage + rr * RBF + ((chunk ^ (rr & 31)) << 4)) =
+                    make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+              }
+            }
+            fence_proxy_async_smem();   // the rows are visible to the bulk copy
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_st);
+          alive = mbar_wait_warp(bar_st, st_phase, abort_flag);
+          st_phase ^= 1;
+          if (!alive) break;
+          if (r == hb * 64) {
+            bulk_store(p.part_o + (slot * BM + i * SUB + hb * 64) * HD, stage_u, 64 * RBF);
+            bulk_commit();
+            bulk_wait_all();            // the copy has read the buffer and written scratch
+            fence_proxy_async_all();
+            __threadfence();            // ... device-wide, before this CTA's arrival is counted
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_st);
+          alive = mbar_wait_warp(bar_st, st_phase, abort_flag);
+          st_phase ^= 1;
         }
+        __threadfence();                // (m, l) of this row
+#ifdef MSGL_TRACE
+        if (tid == 0) MSGL_TR(15, clock64());
+#endif
       }
     }
     if (!alive && p.status && r == 0) atomicExch(p.status, 1);
+#ifdef MSGL_TRACE
+    if (tid == 0) MSGL_TR(7, clock64());               // output written
+#endif
   }
 
   // ---- teardown: every role is past its last TMEM access
   tc_fence_before();
   __syncthreads();
+#ifdef MSGL_TRACE
+  if (tid == 0) {
+    MSGL_TR(8, clock64());
+    MSGL_TR(10, trace_wall());
+  }
+#endif
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, Shape::kTmemCols);
   }
-}
 
-// Combines the kv-split partials of one (query token, query head).
-// grid = (total_q, hq), block = HD threads.
-template <typename T, int HD, int BM>
-__global__ void __launch_bounds__(HD) prefill_merge_kernel(const PrefillParams p) {
-  const int tok = blockIdx.x;
-  const int hq = blockIdx.y;
-  // sequence of this token: last b with qo_indptr[b] <= tok
-  int lo = 0, hi = p.batch;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (p.qo_indptr[mid] <= tok) lo = mid; else hi = mid;
-  }
-  const int b = lo;
-  const int q_begin = p.qo_indptr[b];
-  if (tok < q_begin || tok >= p.qo_indptr[b + 1]) return;  // token not covered by any sequence
-  const int G = p.group;
-  const int h = hq / G, g = hq - h * G;
-  const int pk = (tok - q_begin) * G + g;
-  const int qt = pk / BM, r = pk - qt * BM;
-  grid_dependency_wait();  // plan entries and partials come from the attention kernel
-  const int base = p.plan[2 * b], nsplit = p.plan[2 * b + 1];
-  const int d = threadIdx.x;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) {
-    const int64_t slot = static_cast<int64_t>(base + qt * nsplit + s) * p.hkv + h;
-    M = fmaxf(M, p.part_ml[(slot * BM + r) * 2]);
-  }
-  float num = 0.f, den = 0.f;
-  if (M != -INFINITY) {
-    for (int s = 0; s < nsplit; ++s) {
-      const int64_t slot = static_cast<int64_t>(base + qt * nsplit + s) * p.hkv + h;
-      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + (slot * BM + r) * 2);
-      const float w = fast_exp2(ml.x - M);  // exp2(-inf) = 0 for empty splits
-      den += w * ml.y;
-      num += w * p.part_o[(slot * BM + r) * HD + d];
+  // ---- kv splits: the CTA that arrives last at the unit's counter merges the partials
+  // (out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s) and writes the output rows; no second
+  // launch.  The counter goes back to zero for the next call.
+  if (p.kv_chunk > 0 && sq.nsplit > 1) {
+    __shared__ int s_last;
+    const int nsp = sq.nsplit;
+    const int64_t slot0 = static_cast<int64_t>(it.base + qt * nsp) * p.hkv + h;  // split s: slot0 + s * hkv
+    if (tid == 0) {
+      MSGL_TR(11, clock64());
+      int* ticket = p.tickets + (it.qt_base + qt) * p.hkv + h;
+      __threadfence();
+      const int arrived = atomicAdd(ticket, 1);
+      s_last = (arrived == nsp - 1) ? 1 : 0;
+      if (s_last) *ticket = 0;
+    }
+    __syncthreads();
+#ifdef MSGL_TRACE
+    if (tid == 0) {
+      MSGL_TR(12, clock64());
+      MSGL_TR(13, s_last);
+    }
+#endif
+    if (s_last != 0 && warp < kMmaWarp) {
+      // the softmax warps merge (a function of its own: its registers do not weigh on the main loop)
+      const MergeArgs ma{p.part_o, p.part_ml, p.out, p.gate, p.status, p.hq, p.hkv, p.group};
+      merge_kv_splits<T, HD, NSUB, kMmaWarp, Shape>(ma, bars, smem_raw, smem0, abort_flag, nsp, slot0,
+                                                    rows_valid, pk0, sq.q_begin, h);
+#ifdef MSGL_TRACE
+      if (tid == 0) MSGL_TR(14, clock64());
+#endif
     }
   }
-  const int64_t oi = (static_cast<int64_t>(tok) * p.hq + hq) * HD + d;
-  const float val = den > 0.f ? num / den : 0.f;
-  static_cast<T*>(p.out)[oi] =
-      p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[oi]) : MmaOp<T>::from_float(val);
 }
 
 }  // namespace msgl

@@ -30,8 +30,12 @@ __all__ = [
 
 _DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
 
-# scratch per (device index, stream handle); grown on demand, never shrunk
-_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+# scratch per (device index, stream handle, operator); grown on demand, never shrunk.  The
+# operators keep arrival counters in their scratch that must read zero when a call starts (the
+# kernels put them back to zero), so a buffer is zero-filled once, on the stream that will use
+# it, and never shared between operators.
+_workspaces: Dict[Tuple[int, int, str], torch.Tensor] = {}
+_retired: list = []   # outgrown buffers stay alive: work queued on their stream may still use them
 
 
 def _stream_handle(stream, device: torch.device) -> int:
@@ -42,12 +46,17 @@ def _stream_handle(stream, device: torch.device) -> int:
     return int(stream)
 
 
-def _workspace(nbytes: int, device: torch.device, stream_handle: int) -> torch.Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_handle)
+def _workspace(nbytes: int, device: torch.device, stream_handle: int, kind: str) -> torch.Tensor:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, stream_handle, kind)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        # zero-filled so that the device status word at its head starts clear
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            _retired.append(ws)
+        # allocated and zero-filled on the stream the kernels will run on, so that the fill is
+        # ordered before them even when that stream is not torch's current one
+        with torch.cuda.stream(torch.cuda.ExternalStream(stream_handle, device=device)):
+            ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -119,7 +128,7 @@ def paged_decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_sp
     lib = _lib.lib()
     with torch.cuda.device(q.device):
         need = lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits))
-        ws = _workspace(need, q.device, sh)
+        ws = _workspace(need, q.device, sh, "decode")
         tail = (out.data_ptr(), ws.data_ptr(), ws.numel(), batch, hq, k_cache.shape[1], d,
                 k_cache.shape[0], _DTYPES[q.dtype], float(sm_scale), int(max_kv_splits), sh)
         head = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kv_indptr.data_ptr(),
@@ -162,7 +171,7 @@ def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indice
     with torch.cuda.device(q.device):
         need = lib.msgl_prefill_workspace_bytes(batch, total_q, total_kv, hq, k_cache.shape[1], d,
                                                 int(max_len_extend), int(sliding_window_size))
-        ws = _workspace(need, q.device, sh)
+        ws = _workspace(need, q.device, sh, "prefill")
         head = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
                 kv_indptr.data_ptr(), kv_indices.data_ptr(), prefix_lens.data_ptr())
         tail = (out.data_ptr(), ws.data_ptr(), ws.numel(), batch, total_q, total_kv, hq, k_cache.shape[1],
@@ -202,7 +211,7 @@ def paged_decode_attention_p16(q, k_cache, v_cache, page_indptr, page_indices, k
     with torch.cuda.device(q.device):
         need = ((lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits)) + 255) // 256 * 256
                 + lib.msgl_page_index_workspace_bytes(batch, total_pages, int(page_size)))
-        ws = _workspace(need, q.device, sh)
+        ws = _workspace(need, q.device, sh, "decode")
         _lib.check(lib.msgl_paged_decode_attention_p16(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_indptr.data_ptr(),
             page_indices.data_ptr(), kv_lens.data_ptr(), num_kv_splits.data_ptr(), out.data_ptr(),
@@ -237,7 +246,7 @@ def paged_prefill_attention_p16(q, k_cache, v_cache, qo_indptr, page_indptr, pag
         need = lib.msgl_prefill_workspace_bytes_p16(batch, total_q, total_pages, int(page_size), hq,
                                                     k_cache.shape[1], d, int(max_len_extend),
                                                     int(sliding_window_size))
-        ws = _workspace(need, q.device, sh)
+        ws = _workspace(need, q.device, sh, "prefill")
         _lib.check(lib.msgl_paged_prefill_attention_p16(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
             page_indptr.data_ptr(), page_indices.data_ptr(), kv_lens.data_ptr(), prefix_lens.data_ptr(),
@@ -278,9 +287,11 @@ def store_kv_cache(k_cache, v_cache, indices, k, v, *, stream=None) -> None:
     _require(indices.is_contiguous(), f"{op}: indices must be contiguous")
     sh = _stream_handle(stream, k_cache.device)
     with torch.cuda.device(k_cache.device):
+        status = _workspace(256, k_cache.device, sh, "decode")   # dropped rows are reported there
         _lib.check(_lib.lib().msgl_store_kv_cache(
             k_cache.data_ptr(), v_cache.data_ptr(), indices.data_ptr(), k.data_ptr(), v.data_ptr(),
-            length, hkv, d, num_slots, k_cache.stride(0), k.stride(0), _DTYPES[k_cache.dtype], sh))
+            length, hkv, d, num_slots, k_cache.stride(0), k.stride(0), _DTYPES[k_cache.dtype],
+            status.data_ptr(), sh))
 
 
 def qk_norm_rope_store(q, k, v, q_weight, k_weight, positions, out_loc, k_cache, v_cache, *,
@@ -349,9 +360,11 @@ def gather_kv_indices(page_table, table_idx, kv_indptr, total_kv: int, *, stream
     out = torch.empty(int(total_kv), dtype=torch.int32, device=page_table.device)
     sh = _stream_handle(stream, page_table.device)
     with torch.cuda.device(page_table.device):
+        status = _workspace(256, page_table.device, sh, "decode")
         _lib.check(_lib.lib().msgl_gather_kv_indices(
             page_table.data_ptr(), page_table.stride(0), table_idx.contiguous().data_ptr(),
-            kv_indptr.contiguous().data_ptr(), out.data_ptr(), batch, int(total_kv), sh))
+            kv_indptr.contiguous().data_ptr(), out.data_ptr(), batch, int(total_kv),
+            page_table.shape[0], page_table.shape[1], status.data_ptr(), sh))
     return out
 
 

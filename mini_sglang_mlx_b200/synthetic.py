@@ -53,6 +53,17 @@ class Workload:
     def batch(self) -> int:
         return len(self.kv_lens)
 
+    def page_csr(self):
+        """(page_indptr, page_indices, kv_lens) int32 on the workload's device: the page-granular
+        form of ``kv_indptr`` / ``kv_indices`` (one id per 16-token page)."""
+        need = [(l + PAGE_SIZE - 1) // PAGE_SIZE for l in self.kv_lens]
+        dev = self.q.device
+        table = self.page_table
+        parts = [table[b, :n] for b, n in enumerate(need)]
+        idx = torch.cat(parts).contiguous() if parts else torch.zeros(0, dtype=torch.int32, device=dev)
+        return (_indptr(need).to(dev), idx.to(torch.int32),
+                torch.tensor(self.kv_lens, dtype=torch.int32, device=dev))
+
     # ---- algorithmic work: K+V of the visible keys once per KV head, Q and O once,
     # one int32 index per visible key token
     def visible_keys_per_seq(self) -> List[int]:
@@ -65,11 +76,15 @@ class Workload:
             out.append(L - lo)
         return out
 
+    index: str = "token"            # "token": one int32 id per KV token; "page": one per 16-token page
+
     def algorithmic_bytes(self) -> int:
         vis = sum(self.visible_keys_per_seq())
         kv = 2 * vis * self.hkv * self.head_dim * 2
         qo = 2 * self.q.shape[0] * self.hq * self.head_dim * 2
-        return kv + qo + 4 * vis
+        ids = vis if self.index == "token" else sum((v + PAGE_SIZE - 1) // PAGE_SIZE
+                                                     for v in self.visible_keys_per_seq())
+        return kv + qo + 4 * ids
 
     def algorithmic_flops(self) -> int:
         if self.kind == "decode":

@@ -34,14 +34,18 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_abi_version():
-    assert _lib.lib().msgl_abi_version() == 1
+    assert _lib.lib().msgl_abi_version() == 2
 
 
 def test_decode_workspace_bytes():
     lib = _lib.lib()
-    # status area + fp32 partials (B,Hq,S,D) + fp32 lse (B,Hq,S)
-    assert lib.msgl_decode_workspace_bytes(8, 16, 128, 32) == 256 + 8 * 16 * 32 * 129 * 4
-    assert lib.msgl_decode_workspace_bytes(0, 16, 128, 32) == 256
+    # header (status word + arrival counters) + fp32 partials (B,Hq,S,D) + fp32 lse (B,Hq,S)
+    header = 256 + 16384 * 4
+    assert lib.msgl_decode_workspace_bytes(8, 16, 128, 32) == header + 8 * 16 * 32 * 129 * 4
+    assert lib.msgl_decode_workspace_bytes(0, 16, 128, 32) == header
+    # more (sequence, head) pairs than the header has counters: a counter region of their own
+    big = lib.msgl_decode_workspace_bytes(2048, 16, 128, 2)
+    assert big == header + 2048 * 16 * 4 + 2048 * 16 * 2 * 129 * 4
 
 
 DEC_OK = dict(batch=2, hq=16, hkv=8, d=128, slots=64, dtype=0, splits=32)
@@ -92,10 +96,10 @@ def test_prefill_rejects_bad_arguments(kw, code, text):
 
 def test_store_rejects_bad_arguments():
     lib = _lib.lib()
-    assert lib.msgl_store_kv_cache(None, None, None, None, None, 4, 8, 126, 64, 8 * 126, 8 * 126, 0, None) == 1
+    assert lib.msgl_store_kv_cache(None, None, None, None, None, 4, 8, 126, 64, 8 * 126, 8 * 126, 0, None, None) == 1
     assert "store_kv_cache: head_dim must be a multiple of 4" in _lib.last_error()
-    assert lib.msgl_store_kv_cache(None, None, None, None, None, 4, 8, 128, 64, 8 * 128, 8 * 128, 7, None) == 2
-    assert lib.msgl_store_kv_cache(None, None, None, None, None, 0, 8, 128, 64, 8 * 128, 8 * 128, 0, None) == 0
+    assert lib.msgl_store_kv_cache(None, None, None, None, None, 4, 8, 128, 64, 8 * 128, 8 * 128, 7, None, None) == 2
+    assert lib.msgl_store_kv_cache(None, None, None, None, None, 0, 8, 128, 64, 8 * 128, 8 * 128, 0, None, None) == 0
 
 
 def test_python_ops_refuse_cpu_tensors():

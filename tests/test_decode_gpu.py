@@ -197,3 +197,16 @@ def test_cfg5a_full_size_properties():
     w.v_cache.mul_(2)
     doubled = run(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, tuned, w.max_kv_splits)
     assert torch.equal(doubled, out * 2)
+
+
+def test_more_sequence_head_pairs_than_the_header_has_counters():
+    """batch * Hq beyond the 16384 arrival counters of the workspace header: the op keeps the
+    counters in a region of its own and clears it on every call."""
+    kv_lens = [130 + (i % 7) * 64 for i in range(2100)]
+    args = make_inputs(kv_lens, 2, 8, seed=12)
+    splits = torch.full((len(kv_lens),), 3, dtype=torch.int32).cuda()
+    for _ in range(2):
+        out = run(*args[:5], splits)
+    pick = [0, 1000, 2099]
+    ref = O.paged_decode_attention_oracle(*args[:5], 1 / math.sqrt(128), seqs=pick)
+    assert_close_to_oracle(out[pick], ref[pick], "decode, 2100 sequences")

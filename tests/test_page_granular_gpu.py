@@ -1,9 +1,11 @@
 """Page-granular index entries (one id per page of page_size tokens) on the GPU.
 
 The reference has one token per page (mini_sglang_mlx/engine/engine.py:103) and per-token
-``kv_indices``; these entries take (page_indptr, page_indices, kv_lens) instead.  Checked
-against the per-token ops on the same pool (decode: bit-exact, same kernels and indices) and
-against the fp32 oracle.
+``kv_indices``; these entries take (page_indptr, page_indices, kv_lens) instead.  With a page
+size that is a multiple of 16 the kernels fetch K/V as TMA boxes straight from the page ids;
+other page sizes build per-token ids on the device first.  Checked against the fp32 oracle
+(every benchmark configuration, ragged and boundary lengths, all mask modes, f16, head_dim 256)
+and against the per-token ops on the same pool.
 """
 import math
 
@@ -36,9 +38,9 @@ def make_pool(kv_lens, page_size, hkv, *, seed=0, d=128, spare_pages=5, dtype=to
     return kc, vc, page_indptr.cuda(), page_indices.cuda(), slots.cuda()
 
 
-@pytest.mark.parametrize("page_size", [1, 16, 64])
-@pytest.mark.parametrize("kv_lens", [[1], [237, 809], [16, 32, 48], [0, 5, 0, 4097], [2048] * 3 + [1]],
-                         ids=str)
+@pytest.mark.parametrize("page_size", [1, 16, 32, 64])
+@pytest.mark.parametrize("kv_lens", [[1], [237, 809], [16, 32, 48], [0, 5, 0, 4097], [2048] * 3 + [1],
+                                     [15, 17, 63, 65, 1023, 1025]], ids=str)
 def test_decode_matches_the_per_token_op_and_the_oracle(page_size, kv_lens):
     from mini_sglang_mlx_b200 import paged_decode_attention, paged_decode_attention_p16
     hkv, hq, d = 4, 16, 128
@@ -57,9 +59,13 @@ def test_decode_matches_the_per_token_op_and_the_oracle(page_size, kv_lens):
     assert_close_to_oracle(out, ref, f"decode p{page_size} {kv_lens}")
 
 
-@pytest.mark.parametrize("page_size", [1, 16])
+@pytest.mark.parametrize("page_size", [1, 16, 32])
 @pytest.mark.parametrize("case", [
     dict(q_lens=[5, 17], prefix=[0, 40]),
+    dict(q_lens=[1, 16, 15, 17], prefix=[0, 0, 1, 47]),
+    dict(q_lens=[300, 64], prefix=[129, 8000]),
+    dict(q_lens=[700], prefix=[0], window=100),
+    dict(q_lens=[16, 16], prefix=[8176, 5000], window=4096, cross=True),
     dict(q_lens=[512], prefix=[1000]),
     dict(q_lens=[16] * 4, prefix=[3000, 100, 0, 2047], window=1024),
     dict(q_lens=[8, 8], prefix=[4000, 6000]),                       # short block: key range is split
@@ -122,3 +128,190 @@ def test_workspace_size_is_checked_through_the_c_abi():
         q.data_ptr(), kc.data_ptr(), kc.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
         q.data_ptr(), ws.data_ptr(), ws.numel(), 3, 4, 2, 128, 1600, _lib.DTYPE_BF16, 0.1, 32, 16, 100, 0)
     assert rc != 0 and "workspace too small" in lib.msgl_last_error_string().decode()
+
+
+# ---------------------------------------------------------------- the benchmark configurations
+def _oracle_for(w, seqs=None):
+    if w.kind == "decode":
+        kw = {} if seqs is None else {"seqs": seqs}
+        return O.paged_decode_attention_oracle(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices,
+                                               w.sm_scale, **kw)
+    return O.paged_prefill_attention_oracle(w.q, w.k_cache, w.v_cache, w.qo_indptr, w.kv_indptr,
+                                            w.kv_indices, w.prefix_lens, w.sm_scale,
+                                            is_cross_attention=w.is_cross_attention,
+                                            sliding_window_size=w.sliding_window_size)
+
+
+def _run_paged(w, splits=None):
+    from mini_sglang_mlx_b200 import paged_decode_attention_p16, paged_prefill_attention_p16
+    pip, pidx, lens = w.page_csr()
+    if w.kind == "decode":
+        out = paged_decode_attention_p16(w.q, w.k_cache, w.v_cache, pip, pidx, lens,
+                                         w.num_kv_splits if splits is None else splits, w.sm_scale,
+                                         w.max_kv_splits)
+    else:
+        out = paged_prefill_attention_p16(w.q, w.k_cache, w.v_cache, w.qo_indptr, pip, pidx, lens,
+                                          w.prefix_lens, w.sm_scale, w.max_len_extend,
+                                          is_cross_attention=w.is_cross_attention,
+                                          sliding_window_size=w.sliding_window_size)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg3", "cfg3_cross", "cfg4", "cfg5b_128_1024",
+                                  "cfg5b_128_32768", "cfg5b_1024_4096", "cfg5b_4096_1024"])
+def test_benchmark_configurations_against_the_oracle(name):
+    from mini_sglang_mlx_b200 import synthetic as S
+    from mini_sglang_mlx_b200.kernel import device_status
+    w = {"cfg1": S.cfg1_decode, "cfg2": S.cfg2_prefill, "cfg3": S.cfg3_window_block,
+         "cfg3_cross": lambda: S.cfg3_window_block(cross=True), "cfg4": S.cfg4_verify}.get(name)
+    w = w() if w else S.cfg5b_prefill_point(*map(int, name.split("_")[1:]))
+    device_status()
+    out = _run_paged(w)
+    assert device_status() == 0
+    assert_close_to_oracle(out, _oracle_for(w), f"{name} through the page-granular entry")
+
+
+def test_cfg5a_reduced_against_the_oracle_and_the_per_token_op():
+    from mini_sglang_mlx_b200 import paged_decode_attention, synthetic as S
+    w = S.cfg5a_decode(batch=32)
+    out = _run_paged(w)
+    order = sorted(range(w.batch), key=lambda b: w.kv_lens[b])
+    pick = [order[0], order[len(order) // 2], order[-1]]
+    ref = _oracle_for(w, seqs=pick)
+    assert_close_to_oracle(out[pick], ref[pick], "cfg5a subsample, page-granular")
+    same = paged_decode_attention(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, w.num_kv_splits,
+                                  w.sm_scale, w.max_kv_splits)
+    assert (out.float() - same.float()).abs().max().item() <= 1.6e-2
+
+
+def test_cfg5a_full_size_properties():
+    """The long-context decode batch at full size (38 GB of K/V) through the page-granular entry:
+    split-count invariance, exact doubling with V, and three sequences against the oracle."""
+    from mini_sglang_mlx_b200 import synthetic as S
+    from mini_sglang_mlx_b200.attention import compute_num_kv_splits
+    w = S.cfg5a_decode()
+    tuned = torch.tensor(compute_num_kv_splits(w.kv_lens, w.hkv), dtype=torch.int32).cuda()
+    out = _run_paged(w, tuned)
+    assert torch.isfinite(out.float()).all()
+    assert (out.float() - _run_paged(w).float()).abs().max() <= 1.6e-2
+    order = sorted(range(w.batch), key=lambda b: w.kv_lens[b])
+    pick = [order[0], order[len(order) // 2], order[-1]]
+    ref = _oracle_for(w, seqs=pick)
+    assert_close_to_oracle(out[pick], ref[pick], "cfg5a full size, page-granular, subsample")
+    w.v_cache.mul_(2)
+    assert torch.equal(_run_paged(w, tuned), out * 2)
+
+
+# ---------------------------------------------------------------- edges of the TMA path
+def test_rows_past_a_sequence_end_are_never_used():
+    """The last page of a sequence is ragged; the pool rows behind its last token (and every
+    unowned page) hold NaN here.  Nothing of them may reach the output."""
+    from mini_sglang_mlx_b200 import paged_decode_attention_p16, paged_prefill_attention_p16
+    hkv, hq, d, ps = 2, 8, 128, 16
+    kv_lens = [1, 17, 130, 1000, 2049]
+    q_lens = [1, 9, 64, 8, 300]
+    kc, vc, pip, pidx, slots = make_pool(kv_lens, ps, hkv, seed=21)
+    used = torch.zeros(kc.shape[0], dtype=torch.bool, device="cuda")
+    used[slots.long()] = True
+    kc[~used] = float("nan")
+    vc[~used] = float("nan")
+    lens = torch.tensor(kv_lens, dtype=torch.int32).cuda()
+    indptr = torch.from_numpy(O.build_indptr(kv_lens)).cuda()
+    scale = 1 / math.sqrt(d)
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(len(kv_lens), hq, d, generator=g).bfloat16().cuda()
+    splits = torch.from_numpy(O.compute_num_kv_splits(kv_lens)).cuda()
+    out = paged_decode_attention_p16(q, kc, vc, pip, pidx, lens, splits, scale, 32, page_size=ps)
+    ref = O.paged_decode_attention_oracle(q, kc, vc, indptr, slots, scale)
+    assert_close_to_oracle(out, ref, "decode over a pool with NaN outside the sequences")
+    qp = torch.randn(sum(q_lens), hq, d, generator=g).bfloat16().cuda()
+    qo = torch.from_numpy(O.build_indptr(q_lens)).cuda()
+    pre = torch.tensor([l - t for l, t in zip(kv_lens, q_lens)], dtype=torch.int32).cuda()
+    for cross, window in ((False, 0), (True, 0), (False, 50)):
+        outp = paged_prefill_attention_p16(qp, kc, vc, qo, pip, pidx, lens, pre, scale, max(q_lens),
+                                           page_size=ps, is_cross_attention=cross,
+                                           sliding_window_size=window)
+        refp = O.paged_prefill_attention_oracle(qp, kc, vc, qo, indptr, slots, pre, scale,
+                                                is_cross_attention=cross, sliding_window_size=window)
+        assert_close_to_oracle(outp, refp, f"prefill over a pool with NaN outside (cross={cross}, W={window})")
+
+
+def test_a_page_outside_the_pool_is_reported_and_read_as_zeros():
+    from mini_sglang_mlx_b200 import paged_decode_attention_p16, paged_prefill_attention_p16
+    from mini_sglang_mlx_b200.kernel import device_status
+    hkv, hq, d, ps = 2, 4, 128, 16
+    kv_lens = [100, 40]
+    kc, vc, pip, pidx, _ = make_pool(kv_lens, ps, hkv, seed=4)
+    bad = pidx.clone()
+    bad[2] = kc.shape[0] // ps + 3            # a page id past the pool
+    bad[8] = -2
+    lens = torch.tensor(kv_lens, dtype=torch.int32).cuda()
+    q = torch.randn(2, hq, d).bfloat16().cuda()
+    splits = torch.ones(2, dtype=torch.int32).cuda()
+    device_status()
+    out = paged_decode_attention_p16(q, kc, vc, pip, bad, lens, splits, 0.1, 32, page_size=ps)
+    assert device_status() == 2
+    assert torch.isfinite(out.float()).all()
+    qo = torch.tensor([0, 1, 2], dtype=torch.int32).cuda()
+    pre = torch.tensor([99, 39], dtype=torch.int32).cuda()
+    outp = paged_prefill_attention_p16(q, kc, vc, qo, pip, bad, lens, pre, 0.1, 1, page_size=ps)
+    assert device_status() == 2
+    assert torch.isfinite(outp.float()).all()
+
+
+def test_shared_prefix_pages_and_float16_and_head_dim_256():
+    from mini_sglang_mlx_b200 import paged_decode_attention_p16, paged_prefill_attention_p16
+    ps = 16
+    for d, dtype, hkv, hq in ((128, torch.float16, 2, 8), (256, torch.bfloat16, 2, 8), (256, torch.float16, 1, 4)):
+        kv_lens = [700, 333, 64]
+        q_lens = [60, 13, 64]
+        kc, vc, pip, pidx, slots = make_pool(kv_lens, ps, hkv, seed=d + hq, d=d, dtype=dtype)
+        # sequence 1 re-uses the first 20 pages of sequence 0 (a shared cached prefix)
+        pidx = pidx.clone()
+        start0, start1 = int(pip[0]), int(pip[1])
+        pidx[start1:start1 + 20] = pidx[start0:start0 + 20]
+        slots = slots.clone()
+        o0, o1 = 0, kv_lens[0]
+        slots[o1:o1 + 320] = slots[o0:o0 + 320]
+        lens = torch.tensor(kv_lens, dtype=torch.int32).cuda()
+        indptr = torch.from_numpy(O.build_indptr(kv_lens)).cuda()
+        scale = 1 / math.sqrt(d)
+        g = torch.Generator().manual_seed(d)
+        q = torch.randn(len(kv_lens), hq, d, generator=g).to(dtype).cuda()
+        splits = torch.from_numpy(O.compute_num_kv_splits(kv_lens)).cuda()
+        out = paged_decode_attention_p16(q, kc, vc, pip, pidx, lens, splits, scale, 32, page_size=ps)
+        assert_close_to_oracle(out, O.paged_decode_attention_oracle(q, kc, vc, indptr, slots, scale),
+                               f"decode D={d} {dtype}")
+        qp = torch.randn(sum(q_lens), hq, d, generator=g).to(dtype).cuda()
+        qo = torch.from_numpy(O.build_indptr(q_lens)).cuda()
+        pre = torch.tensor([l - t for l, t in zip(kv_lens, q_lens)], dtype=torch.int32).cuda()
+        outp = paged_prefill_attention_p16(qp, kc, vc, qo, pip, pidx, lens, pre, scale, max(q_lens),
+                                           page_size=ps)
+        refp = O.paged_prefill_attention_oracle(qp, kc, vc, qo, indptr, slots, pre, scale)
+        assert_close_to_oracle(outp, refp, f"prefill D={d} {dtype}")
+
+
+def test_mask_known_answers_through_the_page_entry():
+    """The reference's analytic mask cases (identity slots) with the pool seen as 16-token pages."""
+    from mini_sglang_mlx_b200 import paged_prefill_attention_p16, store_kv_cache
+    from tests.helpers import build_kat_inputs, load_mask_kats
+    ps = 16
+    for case in load_mask_kats():
+        if case["slots"] is not None:
+            continue                      # permuted per-token slots have no page-granular form
+        d = build_kat_inputs(case, device="cuda")
+        npages = (d["kv_len"] + ps - 1) // ps
+        kc = torch.zeros(npages * ps, 1, case["head_dim"], dtype=torch.bfloat16, device="cuda")
+        vc = torch.zeros_like(kc)
+        store_kv_cache(kc, vc, d["kv_indices"], torch.zeros_like(d["v_rows"]), d["v_rows"])
+        pip = torch.tensor([0, npages], dtype=torch.int32).cuda()
+        pidx = torch.arange(npages, dtype=torch.int32).cuda()
+        lens = torch.tensor([d["kv_len"]], dtype=torch.int32).cuda()
+        out = paged_prefill_attention_p16(d["q"], kc, vc, d["qo_indptr"], pip, pidx, lens, d["prefix_lens"],
+                                          d["sm_scale"], case["q_len"], page_size=ps,
+                                          is_cross_attention=case["is_cross_attention"],
+                                          sliding_window_size=case["sliding_window_size"])
+        want = torch.tensor(case["expected_weights"], dtype=torch.float32)
+        got = out.float().cpu()[:, 0, : d["kv_len"]]
+        assert torch.allclose(got, want, rtol=case["rtol"], atol=case["atol"]), case["name"]

@@ -158,3 +158,74 @@ def test_scatter_into_a_pool_beyond_4_gib_per_tensor():
     torch.cuda.synchronize()
     assert torch.equal(kc[idx.long().cuda()], k) and torch.equal(vc[idx.long().cuda()], v)
     assert int((kc != 0).any(dim=(1, 2)).sum()) == len(idx) and int((vc != 0).any(dim=(1, 2)).sum()) == len(idx)
+
+
+def test_rows_with_an_index_outside_the_pool_are_dropped_and_reported():
+    from mini_sglang_mlx_b200 import store_kv_cache
+    from mini_sglang_mlx_b200.kernel import device_status
+    hkv, d, S = 2, 128, 40
+    kc = torch.zeros(S, hkv, d, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    k = torch.randn(4, hkv, d).bfloat16().cuda()
+    v = torch.randn(4, hkv, d).bfloat16().cuda()
+    device_status()
+    store_kv_cache(kc, vc, torch.tensor([3, S, 7, -1], dtype=torch.int32).cuda(), k, v)
+    assert device_status() == 2
+    assert torch.equal(kc[3], k[0]) and torch.equal(vc[7], v[2])
+    assert int((kc != 0).any(dim=(1, 2)).sum()) == 2          # nothing else was written
+    store_kv_cache(kc, vc, torch.tensor([0, 1, 2, 5], dtype=torch.int32).cuda(), k, v)
+    assert device_status() == 0
+
+
+def test_gather_kv_indices_checks_rows_lengths_and_the_output_size():
+    from mini_sglang_mlx_b200 import gather_kv_indices
+    from mini_sglang_mlx_b200.kernel import device_status
+    table = torch.arange(4 * 50, dtype=torch.int32).view(4, 50).cuda()
+    indptr = torch.tensor([0, 10, 30], dtype=torch.int32).cuda()
+    device_status()
+    ok = gather_kv_indices(table, torch.tensor([2, 0], dtype=torch.int32).cuda(), indptr, 30)
+    assert device_status() == 0
+    assert ok.tolist() == list(range(100, 110)) + list(range(0, 20))
+    # a table row that does not exist: skipped and reported, nothing is read
+    gather_kv_indices(table, torch.tensor([2, 9], dtype=torch.int32).cuda(), indptr, 30)
+    assert device_status() == 2
+    # a length beyond the table's columns: clamped and reported
+    long = torch.tensor([0, 10, 80], dtype=torch.int32).cuda()
+    out = gather_kv_indices(table, torch.tensor([2, 0], dtype=torch.int32).cuda(), long, 80)
+    assert device_status() == 2
+    assert out[10:60].tolist() == list(range(0, 50))
+
+
+def test_ops_on_a_stream_that_is_not_the_current_one():
+    """``stream=`` runs the kernels (and the first zero-fill of their scratch) on the given
+    stream; the caller orders it against the streams that made the inputs."""
+    import math
+    from mini_sglang_mlx_b200 import paged_decode_attention, paged_prefill_attention
+    from oracle import paged_attention_oracle as O
+    from tests.helpers import assert_close_to_oracle
+    g = torch.Generator().manual_seed(9)
+    hkv, hq, d = 2, 8, 128
+    kv_lens = [3000, 700]
+    total = sum(kv_lens)
+    kc = torch.randn(total, hkv, d, generator=g).bfloat16().cuda()
+    vc = torch.randn(total, hkv, d, generator=g).bfloat16().cuda()
+    slots = torch.randperm(total, generator=g).int().cuda()
+    indptr = torch.from_numpy(O.build_indptr(kv_lens)).cuda()
+    q = torch.randn(2, hq, d, generator=g).bfloat16().cuda()
+    splits = torch.tensor([8, 3], dtype=torch.int32).cuda()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    out = paged_decode_attention(q, kc, vc, indptr, slots, splits, 1 / math.sqrt(d), 32, stream=side)
+    qo = torch.tensor([0, 8, 16], dtype=torch.int32).cuda()
+    side.wait_stream(torch.cuda.current_stream())
+    qp = torch.randn(16, hq, d, generator=g).bfloat16().cuda()
+    pre = torch.tensor([2992, 692], dtype=torch.int32).cuda()
+    side.wait_stream(torch.cuda.current_stream())
+    outp = paged_prefill_attention(qp, kc, vc, qo, indptr, slots, pre, 1 / math.sqrt(d), 8,
+                                   stream=side.cuda_stream)
+    side.synchronize()
+    assert_close_to_oracle(out, O.paged_decode_attention_oracle(q, kc, vc, indptr, slots, 1 / math.sqrt(d)),
+                           "decode on a side stream")
+    assert_close_to_oracle(outp, O.paged_prefill_attention_oracle(qp, kc, vc, qo, indptr, slots, pre,
+                                                                  1 / math.sqrt(d)),
+                           "prefill (key range split) on a side stream")

@@ -57,6 +57,25 @@ def test_static_scratch_entry_matches_the_workspace_entry_twice_in_a_row():
                                "static-scratch decode")
 
 
+@pytest.mark.gpu
+def test_static_scratch_entry_reports_a_slot_outside_the_pool():
+    """The status word of the built-in array is read (and cleared) with msgl_read_status(NULL)."""
+    import ctypes
+    lib = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    word = ctypes.c_int(-1)
+    assert lib.msgl_read_status(None, 1, ctypes.byref(word), stream) in (0, 7)   # start clean
+    q, kc, vc, indptr, slots, splits = _problem([600, 70], 2, 8, seed=3)
+    bad = slots.clone()
+    bad[5] = kc.shape[0] + 11
+    got = _static(q, kc, vc, indptr, bad, splits)
+    assert torch.isfinite(got.float()).all()
+    assert lib.msgl_read_status(None, 1, ctypes.byref(word), stream) == 7 and word.value == 2
+    assert "outside the pool" in _lib.last_error()
+    _static(q, kc, vc, indptr, slots, splits)
+    assert lib.msgl_read_status(None, 0, ctypes.byref(word), stream) == 0 and word.value == 0
+
+
 def test_static_scratch_entry_rejects_problems_beyond_its_array():
     # 4096 * 32 * 32 partial rows need far more than the 32 MiB the library holds;
     # the check needs no device, so it also runs where there is no GPU
