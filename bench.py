@@ -321,9 +321,10 @@ class E2EPipeline:
 
     def __init__(self, w, be, batch, host, dev, gather):
         self.w, self.be, self.batch, self.host, self.dev, self.gather = w, be, batch, host, dev, gather
-        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream() for _ in range(3))
+        self.s_in, self.s_run, self.s_out, self.s_gather = (torch.cuda.Stream() for _ in range(4))
         self.ev_in = [torch.cuda.Event() for _ in range(2)]
         self.ev_run = [torch.cuda.Event() for _ in range(2)]
+        self.ev_gather = [torch.cuda.Event() for _ in range(2)]
         self.ev_out = [torch.cuda.Event() for _ in range(2)]
         self.i = 0
 
@@ -343,19 +344,45 @@ class E2EPipeline:
             out = self.be.forward(self.dev[k]["q"], self.dev[k]["k"], self.dev[k]["v"], 0, self.batch,
                                   is_cross_attention=w.is_cross_attention,
                                   sliding_window_size=w.sliding_window_size)
-            if self.gather is not None:
-                out = self.gather(out)
             self.ev_run[k].record(self.s_run)
+        if self.gather is not None:
+            # the reassembly of the ranks' outputs runs on a stream of its own, so that the next
+            # step's store and attention do not queue behind the collective
+            with torch.cuda.stream(self.s_gather):
+                self.s_gather.wait_event(self.ev_run[k])
+                out.record_stream(self.s_gather)
+                out = self.gather(out)
+                self.ev_gather[k].record(self.s_gather)
         with torch.cuda.stream(self.s_out):
-            self.s_out.wait_event(self.ev_run[k])
+            self.s_out.wait_event(self.ev_gather[k] if self.gather is not None else self.ev_run[k])
             out.record_stream(self.s_out)
             self.host["out"][k].copy_(out[: self.host["out"][k].shape[0]], non_blocking=True)
             self.ev_out[k].record(self.s_out)
         self.i += 1
 
     def drain(self):
-        for s in (self.s_in, self.s_run, self.s_out):
+        for s in (self.s_in, self.s_run, self.s_gather, self.s_out):
             s.synchronize()
+
+    def copy_floor_ms(self, steps: int, dist_on: bool) -> float:
+        """Per-step time of the bare staging copies alone (this step's inputs host -> device, the
+        output device -> host, on their two streams, nothing else running), all ranks at once:
+        what the end-to-end step cannot go below on this host."""
+        out_dev = torch.empty_like(self.host["out"][0], device=self.dev[0]["staging"].device)
+        barrier(dist_on)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(self.s_in)
+        self.s_out.wait_event(start)
+        for i in range(steps):
+            with torch.cuda.stream(self.s_in):
+                self.dev[i % 2]["staging"].copy_(self.host["staging"], non_blocking=True)
+            with torch.cuda.stream(self.s_out):
+                self.host["out"][i % 2].copy_(out_dev, non_blocking=True)
+        self.s_in.wait_stream(self.s_out)
+        end.record(self.s_in)
+        self.drain()
+        barrier(dist_on)
+        return start.elapsed_time(end) / steps
 
 
 def bind_near_gpu(index: int):
@@ -413,7 +440,8 @@ def _time_e2e(w, device, steps, warmup, dist_on, world):
     barrier(dist_on)
     ms = start.elapsed_time(end)
     bi, bo = e2e_bytes(w, host, batch)
-    return ms, bi, bo
+    floor = pipe.copy_floor_ms(steps, dist_on)
+    return ms, bi, bo, floor
 
 
 # ----------------------------------------------------------------------------- CPU baseline
@@ -551,14 +579,122 @@ def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, pea
         res["cuda_graph"] = "each step replays one captured operator call"
     if with_e2e:
         e_steps = max(3, min(steps, 50))
-        ms, bi, bo = time_e2e(w, device, e_steps, min(warmup, 5), dist_on, world)
+        ms, bi, bo, floor = time_e2e(w, device, e_steps, min(warmup, 5), dist_on, world)
         ms = max_over_ranks(ms, dist_on)
+        floor = max_over_ranks(floor, dist_on)
         res["e2e"] = {"value": work_all * e_steps / (ms * 1e-3) / div, "unit": unit,
                       "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo, "steps": e_steps,
-                      "ms_per_step": ms / e_steps, "cpu_binding": NUMA_NOTE,
+                      "ms_per_step": ms / e_steps, "copy_floor_ms": floor, "cpu_binding": NUMA_NOTE,
                       "pipelining": "copies and compute of neighbouring steps overlap "
-                                    "(3 streams, 2 buffers); one host wait per step"}
+                                    "(copy-in, compute, gather, copy-out streams, 2 buffers); one "
+                                    "host wait per step; copy_floor_ms = the bare staging copies of "
+                                    "all ranks at once, no compute"}
     return w, res
+
+
+# ----------------------------------------------------------------------------- strong scaling
+def _timed_steps(call, steps, dist_on):
+    """Device time (ms) of `steps` calls in a row, max over ranks."""
+    for _ in range(3):
+        call()
+    barrier(dist_on)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        out = call()
+    end.record()
+    barrier(dist_on)
+    return max_over_ranks(start.elapsed_time(end), dist_on) / steps, out
+
+
+def sharded_decode(device, rank, world, steps):
+    """ONE global long-context decode batch (cfg5a) split over the ranks by request
+    (`parallel.assign_requests`: longest first onto the least loaded rank).  A rank's pool holds the
+    pages of its own sequences only (same values as in the global pool, freshly permuted), with its
+    own page index and lengths; the outputs are reassembled with `parallel.gather_request_outputs`
+    (one NCCL all-gather); rank 0 also runs the unsharded batch and compares bit for bit."""
+    from mini_sglang_mlx_b200 import paged_decode_attention_p16, parallel as P, synthetic as S
+    from mini_sglang_mlx_b200.attention import compute_num_kv_splits
+    w = S.cfg5a_decode(seed=505, device=device)
+    w.index = "page"
+    splits_all = compute_num_kv_splits(w.kv_lens, w.hkv)
+    shards = P.assign_requests(w.kv_lens, world)
+    mine = shards[rank]
+    need = [(w.kv_lens[b] + S.PAGE_SIZE - 1) // S.PAGE_SIZE for b in mine]
+    src_pages = torch.cat([w.page_table[b, :n] for b, n in zip(mine, need)]).long()
+    n_local = int(src_pages.numel())
+    g = torch.Generator().manual_seed(9000 + rank)
+    place = torch.randperm(n_local + 16, generator=g)[:n_local].to(device)      # where each page goes
+    shape = (w.k_cache.shape[0] // S.PAGE_SIZE, S.PAGE_SIZE, w.hkv, w.head_dim)
+    pools = []
+    for full in (w.k_cache, w.v_cache):
+        local = torch.zeros((n_local + 16, *shape[1:]), dtype=full.dtype, device=device)
+        local[place] = full.view(shape)[src_pages]
+        pools.append(local.view(-1, w.hkv, w.head_dim))
+    kc, vc = pools
+    q = w.q[mine].contiguous()
+    pip = S._indptr(need).to(device)
+    pidx = place.to(torch.int32)
+    lens = torch.tensor([w.kv_lens[b] for b in mine], dtype=torch.int32, device=device)
+    splits = torch.tensor([splits_all[b] for b in mine], dtype=torch.int32, device=device)
+    reference = None
+    if rank == 0:
+        gp, gi, gl = w.page_csr()
+        reference = paged_decode_attention_p16(w.q, w.k_cache, w.v_cache, gp, gi, gl,
+                                               torch.tensor(splits_all, dtype=torch.int32, device=device),
+                                               w.sm_scale, w.max_kv_splits)
+        torch.cuda.synchronize()
+    total_bytes = w.algorithmic_bytes()
+    per_token = 2 * w.hkv * w.head_dim * 2
+    rank_bytes = [sum(w.kv_lens[b] for b in s) * per_token for s in shards]
+    kv_lens, batch, name = list(w.kv_lens), w.batch, w.name
+    del w, full, local, pools
+    torch.cuda.empty_cache()
+
+    call = lambda: paged_decode_attention_p16(q, kc, vc, pip, pidx, lens, splits, 1 / math.sqrt(128), 32)  # noqa: E731
+    ms, out_local = _timed_steps(call, steps, True)
+    plan = P.GatherPlan(shards, [1] * batch, device)
+    gather = lambda: P.gather_request_outputs(out_local, plan)  # noqa: E731
+    gms, full_out = _timed_steps(gather, 3, True)
+    exact = bool(torch.equal(full_out, reference)) if rank == 0 else None
+    return {"workload": name, "split": "by request: parallel.assign_requests, longest first onto the "
+                                       "least loaded rank; per-rank pool, page index and lengths",
+            "scaling": "strong", "value": total_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
+            "ms_per_step": ms, "reassembly_ms": gms,
+            "value_with_reassembly": total_bytes / ((ms + gms) * 1e-3) / 1e9,
+            "load_imbalance_max_over_mean": max(rank_bytes) / (sum(rank_bytes) / world),
+            "sequences_per_rank": [len(s) for s in shards],
+            "matches_unsharded_bit_for_bit": exact, "steps": steps}
+
+
+def sharded_by_head(device, rank, world, steps):
+    """The batch-1 fallback: one prefill grid point (chunk 2048 after a 8192-token prefix) split
+    by KV-head group (`parallel.head_slices`); each rank holds the K/V heads of its group for all
+    tokens; `parallel.gather_head_outputs` concatenates along the head axis.  Rank 0 compares with
+    the unsharded op (same rows and heads; the key-range split may differ, so within the parity
+    tolerance rather than bit for bit)."""
+    from mini_sglang_mlx_b200 import paged_prefill_attention_p16, parallel as P, synthetic as S
+    w = S.cfg5b_prefill_point(2048, 8192, device=device)
+    if w.hkv % world != 0:
+        return {"workload": w.name, "skipped": f"{w.hkv} KV heads do not split over {world} ranks"}
+    qs, ks = P.head_slices(w.hq, w.hkv, world)[rank]
+    q = w.q[:, qs].contiguous()
+    kc, vc = w.k_cache[:, ks].contiguous(), w.v_cache[:, ks].contiguous()
+    pip, pidx, lens = w.page_csr()
+
+    def run(q_, kc_, vc_):
+        return paged_prefill_attention_p16(q_, kc_, vc_, w.qo_indptr, pip, pidx, lens, w.prefix_lens,
+                                           w.sm_scale, w.max_len_extend)
+    ms, out_local = _timed_steps(lambda: run(q, kc, vc), steps, True)
+    gms, full_out = _timed_steps(lambda: P.gather_head_outputs(out_local), 3, True)
+    err = None
+    if rank == 0:
+        err = float((full_out.float() - run(w.q, w.k_cache, w.v_cache).float()).abs().max())
+    flops = w.algorithmic_flops()
+    return {"workload": w.name, "split": "by KV-head group: parallel.head_slices", "scaling": "strong",
+            "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+            "reassembly_ms": gms, "value_with_reassembly": flops / ((ms + gms) * 1e-3) / 1e12,
+            "max_abs_diff_to_unsharded": err, "tolerance": 2e-2, "steps": steps}
 
 
 def run_ours(args):
@@ -591,6 +727,13 @@ def run_ours(args):
             del w2
             torch.cuda.empty_cache()
 
+    if dist_on and not args.no_sharded:
+        torch.cuda.empty_cache()
+        ssteps = max(3, min(args.steps, 20))
+        extra["sharded"] = {"decode": sharded_decode(device, rank, world, ssteps),
+                            "prefill_by_head": sharded_by_head(device, rank, world, ssteps)}
+        torch.cuda.empty_cache()
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(make_workload(args.workload, device, rank))
@@ -600,7 +743,9 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": main["workload"], "sharding": "by request, one batch per GPU",
+            "config": {"workload": main["workload"],
+                       "sharding": "value/e2e: by request, one batch per GPU (weak scaling); "
+                                   "\"sharded\": one global batch split over the GPUs (strong scaling)",
                        "l2": main["l2"], "page_size": 16,
                        "index_granularity": ("one id per 16-token page (TMA box loads)" if INDEX == "page"
                                              else "per-token slot ids"),
@@ -812,6 +957,8 @@ def main():
     ap.add_argument("--graph", action="store_true",
                     help="kernel timing replays a CUDA graph of one operator call (launch overhead apart)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-sharded", action="store_true",
+                    help="N > 1: skip the strong-scaling section (one global batch split over the ranks)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
     ap.add_argument("--index", default="page", choices=["page", "token"],
                     help="kernel-only timing through the page-granular operators (one id per 16-token "

@@ -48,34 +48,49 @@ def head_slices(num_q_heads: int, num_kv_heads: int, world_size: int) -> List[Tu
             for r in range(world_size)]
 
 
-def gather_request_outputs(local_out: torch.Tensor, shards: List[List[int]],
-                           rows_per_request: Sequence[int], group=None) -> torch.Tensor:
+class GatherPlan:
+    """Where every request's rows sit in the all-gathered buffer: computed once per batch
+    (host), then each reassembly is one collective and one row gather on the device."""
+
+    def __init__(self, shards: List[List[int]], rows_per_request: Sequence[int], device=None):
+        counts = [sum(rows_per_request[i] for i in s) for s in shards]
+        self.width = max(counts) if counts else 0
+        self.local_rows = counts
+        starts = [0]
+        for n in rows_per_request:
+            starts.append(starts[-1] + n)
+        src = [0] * starts[-1]
+        for r, shard in enumerate(shards):
+            off = r * self.width
+            for i in shard:
+                n = rows_per_request[i]
+                for k in range(n):
+                    src[starts[i] + k] = off + k
+                off += n
+        self.index = torch.tensor(src, dtype=torch.int64, device=device)
+
+
+def gather_request_outputs(local_out: torch.Tensor, shards, rows_per_request: Sequence[int] = None,
+                           group=None) -> torch.Tensor:
     """All ranks' output rows in original request order.
 
     ``local_out`` holds this rank's rows, requests in the order of
     ``shards[rank]``; request i owns ``rows_per_request[i]`` rows (1 for decode,
     its query length for prefill).  Shards are padded to the largest one so a
-    single ``all_gather_into_tensor`` suffices."""
+    single ``all_gather_into_tensor`` suffices.  ``shards`` may be a ``GatherPlan``
+    built once for the batch (then ``rows_per_request`` is not needed)."""
+    plan = shards if isinstance(shards, GatherPlan) else GatherPlan(shards, rows_per_request,
+                                                                    local_out.device)
     world = dist.get_world_size(group)
-    counts = [sum(rows_per_request[i] for i in s) for s in shards]
-    width = max(counts) if counts else 0
     tail = local_out.shape[1:]
-    padded = local_out.new_zeros((width, *tail))
-    padded[: local_out.shape[0]] = local_out
-    gathered = local_out.new_empty((world * width, *tail))
+    if local_out.shape[0] == plan.width:
+        padded = local_out.contiguous()
+    else:
+        padded = local_out.new_zeros((plan.width, *tail))
+        padded[: local_out.shape[0]] = local_out
+    gathered = local_out.new_empty((world * plan.width, *tail))
     dist.all_gather_into_tensor(gathered, padded, group=group)
-    total = sum(rows_per_request)
-    full = local_out.new_empty((total, *tail))
-    starts = [0]
-    for n in rows_per_request:
-        starts.append(starts[-1] + n)
-    for r, shard in enumerate(shards):
-        off = r * width
-        for i in shard:
-            n = rows_per_request[i]
-            full[starts[i]:starts[i] + n] = gathered[off:off + n]
-            off += n
-    return full
+    return gathered.index_select(0, plan.index.to(gathered.device))
 
 
 def gather_head_outputs(local_out: torch.Tensor, group=None) -> torch.Tensor:
