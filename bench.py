@@ -266,7 +266,7 @@ def build_e2e(w, device):
     indptr = w.kv_indptr.tolist()
     for b in range(w.batch):
         table[b, : w.kv_lens[b]] = w.kv_indices[indptr[b]:indptr[b + 1]]
-    be = AttnBackend(_ModelCfg(w), pool, table)
+    be = AttnBackend(_ModelCfg(w), pool, table, page_size=16 if INDEX == "page" else 1)
     if w.kind == "decode":
         reqs = [Req(table_idx=b, cached_len=w.kv_lens[b] - 1, device_len=w.kv_lens[b]) for b in range(w.batch)]
         phase = BatchPhase.DECODE

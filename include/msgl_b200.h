@@ -241,6 +241,29 @@ int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,
                            int64_t table_cols, void* status_word, void* stream);
 
 /*
+ * All index arrays of one step from the page table in ONE launch (one host-to-device copy of
+ * `req` in front of it).  req (3 * batch int32, device): for the batch's sequences in order the
+ * number of new tokens [0, batch), the KV lengths including them [batch, 2 batch) and the
+ * page-table rows [2 batch, 3 batch) (a decode step has one new token per sequence).  Outputs:
+ * qo_indptr / kv_indptr (batch+1), prefix_lens = kv - new (batch), num_kv_splits =
+ * min(max_kv_splits, max(1, ceil(kv / split_chunk))) (batch; split_chunk 0 = the reference's 128),
+ * positions (total_q: kv - new + i for the i-th new token), kv_indices (total_kv per-token slot
+ * ids copied from the table rows; NULL to skip) and, with page_size > 1, page_indptr (batch+1)
+ * and page_indices (total_pages: slot of the page's first token / page_size; both NULL to
+ * skip).  total_* are the sizes the caller allocated; anything outside them or outside the
+ * table sets status_word (a device int, may be NULL) to 2 and is skipped.
+ * Replaces the host loops of AttnBackend.build_prefill_metadata / build_decode_metadata and
+ * _compute_num_kv_splits (mini_sglang_mlx/attention/backend.py:205-307).
+ */
+int msgl_build_attn_metadata(const int32_t* req, const int32_t* page_table, int64_t table_row_stride,
+                             int64_t table_rows, int64_t table_cols, int batch, int page_size,
+                             int split_chunk, int max_kv_splits, int64_t total_q, int64_t total_kv,
+                             int64_t total_pages, int32_t* qo_indptr, int32_t* kv_indptr,
+                             int32_t* prefix_lens, int32_t* num_kv_splits, int32_t* positions,
+                             int32_t* kv_indices, int32_t* page_indptr, int32_t* page_indices,
+                             void* status_word, void* stream);
+
+/*
  * Page-granular index entries.  The reference hard-wires one token per page
  * (mini_sglang_mlx/engine/engine.py:103) and hands the ops one slot id per token
  * (kv_indices, mini_sglang_mlx/attention/backend.py:239-244, 279-284).  A pool
@@ -271,7 +294,8 @@ size_t msgl_page_index_workspace_bytes(int batch, int64_t total_pages, int page_
 int msgl_paged_decode_attention_p16(
     const void* q, const void* k_cache, const void* v_cache,
     const int32_t* page_indptr, const int32_t* page_indices, const int32_t* kv_lens,
-    const int32_t* num_kv_splits, void* out, void* workspace, size_t workspace_bytes,
+    const int32_t* num_kv_splits, const void* gate /* may be NULL, see *_gated */,
+    void* out, void* workspace, size_t workspace_bytes,
     int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t num_slots,
     int dtype, float sm_scale, int max_kv_splits, int page_size, int64_t total_pages,
     void* stream);
@@ -283,7 +307,8 @@ size_t msgl_prefill_workspace_bytes_p16(int batch, int total_q, int64_t total_pa
 int msgl_paged_prefill_attention_p16(
     const void* q, const void* k_cache, const void* v_cache,
     const int32_t* qo_indptr, const int32_t* page_indptr, const int32_t* page_indices,
-    const int32_t* kv_lens, const int32_t* prefix_lens, void* out, void* workspace,
+    const int32_t* kv_lens, const int32_t* prefix_lens, const void* gate /* may be NULL */,
+    void* out, void* workspace,
     size_t workspace_bytes, int batch, int total_q, int num_q_heads, int num_kv_heads,
     int head_dim, int64_t num_slots, int dtype, float sm_scale, int max_len_extend,
     int is_cross_attention, int sliding_window_size, int page_size, int64_t total_pages,

@@ -38,11 +38,14 @@ SIGNATURES = {
     "msgl_prefill_workspace_bytes": (_sz, [_i, _i, _i64, _i, _i, _i, _i, _i]),
     "msgl_page_index_workspace_bytes": (_sz, [_i, _i64, _i]),
     "msgl_paged_decode_attention_p16": (
-        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i64, _i, _f, _i,
+        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i64, _i, _f, _i,
              _i, _i64, _vp]),
+    "msgl_build_attn_metadata": (
+        _i, [_vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp,
+             _vp, _vp, _vp, _vp, _vp]),
     "msgl_prefill_workspace_bytes_p16": (_sz, [_i, _i, _i64, _i, _i, _i, _i, _i, _i]),
     "msgl_paged_prefill_attention_p16": (
-        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64, _i,
+        _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64, _i,
              _f, _i, _i, _i, _i, _i64, _vp]),
     "msgl_paged_prefill_attention": (
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i64, _i, _i, _i, _i64,

@@ -5,10 +5,17 @@ Mirror of the reference's ``AttnBackend``
 names and the same meaning of every argument, over CUDA ``torch.Tensor``.
 Differences, all inside the boundary:
 
-* ``kv_indices`` is gathered from the device-resident page table by one kernel
-  launch instead of a per-request slice-and-concatenate loop on the host
-  (reference lines 239-244 and 279-284); only the (batch+1)-sized pointer
-  arrays are built on the host and copied.
+* every index array of a step (``qo_indptr``, ``kv_indptr``, ``kv_indices``,
+  ``prefix_lens``, ``positions``, ``num_kv_splits``) comes from ONE launch over the
+  device-resident page table after ONE host-to-device copy of the per-request
+  lengths and table rows (pinned staging), instead of per-request loops and several
+  small copies on the host (reference lines 205-307).
+* ``page_size`` > 1 (the reference has one token per page,
+  mini_sglang_mlx/engine/engine.py:103): the table rows hold page-structured slots
+  (``CacheManager(page_size=...)``), the metadata also carries one id per page
+  (``page_indptr`` / ``page_indices`` / ``kv_lens``) and, when the page size is a
+  multiple of 16, attention runs through the page-granular operators whose kernels
+  fetch K/V as TMA boxes.
 * ``num_kv_splits`` is chosen for a 148-SM part from the batch's total work
   (``compute_num_kv_splits``); ``policy="reference"`` keeps the reference rule
   ``min(32, max(1, ceil(L/128)))`` (lines 304-307).  The result of the decode
@@ -23,8 +30,8 @@ from typing import List, Optional, Sequence
 import torch
 
 from .. import _lib
-from ..kernel import (gather_kv_indices, paged_decode_attention, paged_prefill_attention,
-                      qk_norm_rope_store)
+from ..kernel import (build_attn_metadata, paged_decode_attention, paged_decode_attention_p16,
+                      paged_prefill_attention, paged_prefill_attention_p16, qk_norm_rope_store)
 
 MAX_KV_SPLITS = 32
 
@@ -44,6 +51,11 @@ class PrefillMetadata(BaseAttnMetadata):
     kv_indices: torch.Tensor    # (total_kv,) int32 slot ids
     prefix_lens: torch.Tensor   # (batch,) int32
     max_len_extend: int
+    # page-granular form (None with one token per page)
+    page_indptr: Optional[torch.Tensor] = None   # (batch + 1,) int32
+    page_indices: Optional[torch.Tensor] = None  # (total_pages,) int32 page ids
+    kv_lens: Optional[torch.Tensor] = None       # (batch,) int32
+    page_size: int = 1
 
     def get_last_indices(self, bs: int) -> torch.Tensor:
         return self.qo_indptr[1:1 + bs] - 1
@@ -55,6 +67,10 @@ class DecodeMetadata(BaseAttnMetadata):
     kv_indices: torch.Tensor    # (total_kv,) int32 slot ids
     num_kv_splits: torch.Tensor  # (batch,) int32
     max_kv_splits: int
+    page_indptr: Optional[torch.Tensor] = None
+    page_indices: Optional[torch.Tensor] = None
+    kv_lens: Optional[torch.Tensor] = None
+    page_size: int = 1
 
     def get_last_indices(self, bs: int) -> torch.Tensor:
         return torch.arange(bs, dtype=torch.int32, device=self.kv_indptr.device)
@@ -82,24 +98,34 @@ def compute_num_kv_splits(kv_lens: Sequence[int], num_kv_heads: int, *, sm_count
     return [min(max_kv_splits, max(1, -(-l // chunk))) for l in kv_lens]
 
 
-def _build_indptr(lens: Sequence[int], device) -> torch.Tensor:
-    cs = [0]
-    for l in lens:
-        cs.append(cs[-1] + int(l))
-    return torch.tensor(cs, dtype=torch.int32).to(device, non_blocking=True)
+def split_chunk_tokens(total_kv: int, num_kv_heads: int, *, sm_count: int = 148,
+                       policy: str = "b200") -> int:
+    """Tokens per split of ``compute_num_kv_splits`` for a batch with ``total_kv`` KV tokens."""
+    if policy == "reference":
+        return 128
+    chunk = -(-total_kv * num_kv_heads // (sm_count * 16))
+    chunk = min(4096, max(256, chunk))
+    return -(-chunk // 64) * 64
 
 
 class AttnBackend:
     """Paged attention backend for B200 using the msgl C-ABI operators."""
 
     def __init__(self, config, kvcache, page_table: torch.Tensor, *,
-                 split_policy: str = "b200") -> None:
+                 split_policy: str = "b200", page_size: int = 1) -> None:
         self.config = config
         self.kvcache = kvcache
         self.page_table = page_table      # (rows, max_seq_len) int32 per-token slot ids, on device
         self.sm_scale = 1.0 / math.sqrt(config.head_dim)
         self.split_policy = split_policy
+        self.page_size = int(page_size)
+        # the page-granular operators are the fast path when their kernels can fetch whole
+        # 16-row boxes; other page sizes keep the per-token ids
+        self._paged_ops = self.page_size % 16 == 0
         self._sm_count: Optional[int] = None
+        self._staging: List[torch.Tensor] = []        # pinned (3, capacity) int32 buffers, in turn
+        self._staging_events: List[torch.cuda.Event] = []
+        self._staging_next = 0
 
     # ------------------------------------------------------------------ forward
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layer_id: int, batch, *,
@@ -124,7 +150,15 @@ class AttnBackend:
 
     def _attend(self, q, k_cache, v_cache, metadata, is_cross_attention: bool,
                 sliding_window_size: int, gate=None) -> torch.Tensor:
+        paged = self._paged_ops and metadata.page_indices is not None
         if isinstance(metadata, PrefillMetadata):
+            if paged:
+                return paged_prefill_attention_p16(
+                    q, k_cache, v_cache, metadata.qo_indptr, metadata.page_indptr, metadata.page_indices,
+                    metadata.kv_lens, metadata.prefix_lens, sm_scale=self.sm_scale,
+                    max_len_extend=metadata.max_len_extend, page_size=metadata.page_size,
+                    is_cross_attention=is_cross_attention, sliding_window_size=sliding_window_size,
+                    gate=gate)
             return paged_prefill_attention(
                 q, k_cache, v_cache, metadata.qo_indptr, metadata.kv_indptr, metadata.kv_indices,
                 metadata.prefix_lens, sm_scale=self.sm_scale, max_len_extend=metadata.max_len_extend,
@@ -132,6 +166,11 @@ class AttnBackend:
         assert isinstance(metadata, DecodeMetadata)
         assert not is_cross_attention and sliding_window_size == 0, (
             "is_cross_attention / sliding_window_size are only supported on the prefill path.")
+        if paged:
+            return paged_decode_attention_p16(
+                q, k_cache, v_cache, metadata.page_indptr, metadata.page_indices, metadata.kv_lens,
+                metadata.num_kv_splits, sm_scale=self.sm_scale, max_kv_splits=metadata.max_kv_splits,
+                page_size=metadata.page_size, gate=gate)
         return paged_decode_attention(
             q, k_cache, v_cache, metadata.kv_indptr, metadata.kv_indices, metadata.num_kv_splits,
             sm_scale=self.sm_scale, max_kv_splits=metadata.max_kv_splits, gate=gate)
@@ -169,50 +208,62 @@ class AttnBackend:
         else:
             batch.attn_metadata = self.build_decode_metadata(reqs)
 
-    def _kv_indices(self, reqs, kv_lens: Sequence[int], kv_indptr: torch.Tensor) -> torch.Tensor:
-        table_idx = torch.tensor([r.table_idx for r in reqs], dtype=torch.int32).to(
-            self.page_table.device, non_blocking=True)
-        return gather_kv_indices(self.page_table, table_idx, kv_indptr, sum(kv_lens))
+    def _stage(self, extend_lens: Sequence[int], kv_lens: Sequence[int], rows: Sequence[int]):
+        """The per-request numbers of a step as a pinned, contiguous (3, batch) int32 tensor and
+        the event to record behind the copy that reads it.  Four buffers take turns; one is
+        written again only after the copy that last read it has finished."""
+        n = len(kv_lens)
+        if not self._staging or self._staging[0].numel() < 3 * n:
+            cap = max(64, 1 << max(n - 1, 0).bit_length())
+            self._staging = [torch.empty(3 * cap, dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._staging_events = [torch.cuda.Event() for _ in range(4)]
+            self._staging_next = 0
+        k = self._staging_next
+        self._staging_next = (k + 1) % len(self._staging)
+        self._staging_events[k].synchronize()
+        req = self._staging[k][: 3 * n].view(3, n)
+        req.copy_(torch.tensor([list(extend_lens), list(kv_lens), list(rows)], dtype=torch.int32))
+        return req, self._staging_events[k]
+
+    def _index_arrays(self, reqs, extend_lens: Sequence[int], kv_lens: Sequence[int], split_chunk: int):
+        req, event = self._stage(extend_lens, kv_lens, [r.table_idx for r in reqs])
+        md = build_attn_metadata(req, self.page_table, total_q=sum(extend_lens), total_kv=sum(kv_lens),
+                                 page_size=self.page_size if self._paged_ops else 1,
+                                 split_chunk=split_chunk, max_kv_splits=MAX_KV_SPLITS,
+                                 per_token_ids=not self._paged_ops)
+        event.record()
+        return md
 
     def build_prefill_metadata(self, reqs, *, extend_lens: Optional[List[int]] = None,
                                kv_lens: Optional[List[int]] = None,
                                positions: Optional[torch.Tensor] = None) -> PrefillMetadata:
         """Reference lines 205-254; ``extend_lens`` / ``kv_lens`` overrides serve a
         virtual extend window such as a K+1-token verify."""
-        dev = self.page_table.device
         if extend_lens is None:
             extend_lens = [req.extend_len for req in reqs]
         if kv_lens is None:
             kv_lens = [req.device_len for req in reqs]
-        cached_lens = [kv_lens[i] - extend_lens[i] for i in range(len(reqs))]
-        if positions is None:
-            positions = torch.cat(
-                [torch.arange(cached_lens[i], kv_lens[i], dtype=torch.int32)
-                 for i in range(len(reqs))]).to(dev, non_blocking=True)
-        qo_indptr = _build_indptr(extend_lens, dev)
-        kv_indptr = _build_indptr(kv_lens, dev)
-        kv_indices = self._kv_indices(reqs, kv_lens, kv_indptr)
-        prefix_lens = torch.tensor(cached_lens, dtype=torch.int32).to(dev, non_blocking=True)
-        return PrefillMetadata(positions=positions, qo_indptr=qo_indptr, kv_indptr=kv_indptr,
-                               kv_indices=kv_indices, prefix_lens=prefix_lens,
-                               max_len_extend=max(extend_lens))
+        md = self._index_arrays(reqs, extend_lens, kv_lens, 0)
+        return PrefillMetadata(positions=md["positions"] if positions is None else positions,
+                               qo_indptr=md["qo_indptr"], kv_indptr=md["kv_indptr"],
+                               kv_indices=md["kv_indices"], prefix_lens=md["prefix_lens"],
+                               max_len_extend=max(extend_lens), page_indptr=md["page_indptr"],
+                               page_indices=md["page_indices"], kv_lens=md["kv_lens"],
+                               page_size=self.page_size if self._paged_ops else 1)
 
     def build_decode_metadata(self, reqs, *, kv_lens: Optional[List[int]] = None,
                               positions: Optional[torch.Tensor] = None) -> DecodeMetadata:
         """Reference lines 256-293."""
-        dev = self.page_table.device
         if kv_lens is None:
             kv_lens = [req.device_len for req in reqs]
-        if positions is None:
-            positions = torch.tensor([req.cached_len for req in reqs], dtype=torch.int32).to(
-                dev, non_blocking=True)
-        kv_indptr = _build_indptr(kv_lens, dev)
-        kv_indices = self._kv_indices(reqs, kv_lens, kv_indptr)
         if self._sm_count is None:
-            with torch.cuda.device(dev):
+            with torch.cuda.device(self.page_table.device):
                 self._sm_count = max(1, _lib.lib().msgl_device_sm_count())
-        splits = compute_num_kv_splits(kv_lens, self.config.num_kv_heads, sm_count=self._sm_count,
-                                       max_kv_splits=MAX_KV_SPLITS, policy=self.split_policy)
-        num_kv_splits = torch.tensor(splits, dtype=torch.int32).to(dev, non_blocking=True)
-        return DecodeMetadata(positions=positions, kv_indptr=kv_indptr, kv_indices=kv_indices,
-                              num_kv_splits=num_kv_splits, max_kv_splits=MAX_KV_SPLITS)
+        chunk = split_chunk_tokens(sum(kv_lens), self.config.num_kv_heads, sm_count=self._sm_count,
+                                   policy=self.split_policy)
+        md = self._index_arrays(reqs, [1] * len(reqs), kv_lens, chunk)
+        return DecodeMetadata(positions=md["positions"] if positions is None else positions,
+                              kv_indptr=md["kv_indptr"], kv_indices=md["kv_indices"],
+                              num_kv_splits=md["num_kv_splits"], max_kv_splits=MAX_KV_SPLITS,
+                              page_indptr=md["page_indptr"], page_indices=md["page_indices"],
+                              kv_lens=md["kv_lens"], page_size=self.page_size if self._paged_ops else 1)

@@ -313,6 +313,94 @@ __global__ void gather_kv_indices_kernel(const int32_t* __restrict__ page_table,
     kv_indices[begin + t] = row[t];
 }
 
+// All index arrays of a step in one launch.  `req` holds, for the batch's sequences in order,
+// the new-token counts, the KV lengths and the page-table rows: [extend | kv | row], 3 * batch
+// int32.  CTA (x, b) sums the lengths of the sequences in front of b (a block-wide reduction:
+// batch^2 / 2 additions in total, nothing next to one K/V tile), CTA (0, b) writes b's entries
+// of the pointer arrays, and all CTAs of b copy its slot ids / page ids and write its
+// positions.  Everything is bounds-checked against the sizes the host allocated; a violation
+// sets status word 2 and is skipped.
+struct MetadataParams {
+  const int32_t* req;
+  const int32_t* page_table;
+  int64_t row_stride, table_rows, table_cols;
+  int batch, page_size, split_chunk, max_kv_splits;
+  int64_t total_q, total_kv, total_pages;
+  int32_t *qo_indptr, *kv_indptr, *prefix_lens, *num_kv_splits, *positions;
+  int32_t *kv_indices;     // may be null
+  int32_t *page_indptr, *page_indices;   // may be null (page_size 1)
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) build_metadata_kernel(const MetadataParams p) {
+  __shared__ long long s_red[3][8];
+  const int b = blockIdx.y, tid = threadIdx.x;
+  const int32_t* ext = p.req;
+  const int32_t* kvl = p.req + p.batch;
+  const int32_t* rows = p.req + 2 * p.batch;
+  long long q0 = 0, k0 = 0, g0 = 0;
+  for (int i = tid; i < b; i += 256) {
+    const int e = max(ext[i], 0), k = max(kvl[i], 0);
+    q0 += e;
+    k0 += k;
+    g0 += (k + p.page_size - 1) / p.page_size;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    q0 += __shfl_xor_sync(0xffffffffu, q0, o);
+    k0 += __shfl_xor_sync(0xffffffffu, k0, o);
+    g0 += __shfl_xor_sync(0xffffffffu, g0, o);
+  }
+  if ((tid & 31) == 0) {
+    s_red[0][tid >> 5] = q0;
+    s_red[1][tid >> 5] = k0;
+    s_red[2][tid >> 5] = g0;
+  }
+  __syncthreads();
+  q0 = k0 = g0 = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    q0 += s_red[0][w];
+    k0 += s_red[1][w];
+    g0 += s_red[2][w];
+  }
+  const int e = max(ext[b], 0), k = max(kvl[b], 0);
+  const int npg = (k + p.page_size - 1) / p.page_size;
+  const long long r = rows[b];
+  bool bad = ext[b] < 0 || kvl[b] < 0 || e > k || r < 0 || r >= p.table_rows || k > p.table_cols ||
+             q0 + e > p.total_q || k0 + k > p.total_kv || (p.page_indices && g0 + npg > p.total_pages);
+  if (blockIdx.x == 0 && tid == 0) {
+    p.qo_indptr[b] = static_cast<int32_t>(q0);
+    p.kv_indptr[b] = static_cast<int32_t>(k0);
+    if (p.page_indptr) p.page_indptr[b] = static_cast<int32_t>(g0);
+    if (b == p.batch - 1) {
+      p.qo_indptr[p.batch] = static_cast<int32_t>(q0 + e);
+      p.kv_indptr[p.batch] = static_cast<int32_t>(k0 + k);
+      if (p.page_indptr) p.page_indptr[p.batch] = static_cast<int32_t>(g0 + npg);
+    }
+    p.prefix_lens[b] = k - e;
+    const int chunk = p.split_chunk > 0 ? p.split_chunk : 128;
+    p.num_kv_splits[b] = min(p.max_kv_splits, max(1, (k + chunk - 1) / chunk));
+    if (bad && p.status) atomicExch(p.status, 2);
+  }
+  if (bad) return;
+  const int32_t* row = p.page_table + r * p.row_stride;
+  const int stride = gridDim.x * 256;
+  for (int t = blockIdx.x * 256 + tid; t < k; t += stride) {
+    const int32_t slot = row[t];
+    if (p.kv_indices) p.kv_indices[k0 + t] = slot;
+    if (p.page_indices && t % p.page_size == 0) {
+      if (slot < 0 || slot % p.page_size != 0) {
+        if (p.status) atomicExch(p.status, 2);     // a sequence that does not start its pages on page boundaries
+        p.page_indices[g0 + t / p.page_size] = -1;
+      } else {
+        p.page_indices[g0 + t / p.page_size] = slot / p.page_size;
+      }
+    }
+  }
+  for (int t = blockIdx.x * 256 + tid; t < e; t += stride) p.positions[q0 + t] = k - e + t;
+}
+
 // Page-granular index entries: kv_indptr = exclusive scan of the sequence lengths (one CTA),
 // then one slot id per token, slot = page * page_size + offset inside the page.  A length that
 // is negative or longer than the sequence's pages is reported in the status word and clamped.
@@ -931,7 +1019,8 @@ static int expand_page_index(const char* op_name, const int32_t* page_indptr,
 
 int msgl_paged_decode_attention_p16(const void* q, const void* k_cache, const void* v_cache,
                                     const int32_t* page_indptr, const int32_t* page_indices,
-                                    const int32_t* kv_lens, const int32_t* num_kv_splits, void* out,
+                                    const int32_t* kv_lens, const int32_t* num_kv_splits,
+                                    const void* gate, void* out,
                                     void* workspace, size_t workspace_bytes, int batch,
                                     int num_q_heads, int num_kv_heads, int head_dim,
                                     int64_t num_slots, int dtype, float sm_scale, int max_kv_splits,
@@ -954,7 +1043,7 @@ int msgl_paged_decode_attention_p16(const void* q, const void* k_cache, const vo
     if (total_pages * page_size >= (1ll << 31))
       return fail(MSGL_BAD_SHAPE, std::string(op) + ": total_pages * page_size must be < 2^31");
     const PageIndex pages{page_indptr, page_indices, kv_lens, page_size};
-    return decode_impl(q, k_cache, v_cache, nullptr, nullptr, num_kv_splits, nullptr, out, workspace,
+    return decode_impl(q, k_cache, v_cache, nullptr, nullptr, num_kv_splits, gate, out, workspace,
                        op_ws, batch, num_q_heads, num_kv_heads, head_dim, num_slots, dtype, sm_scale,
                        max_kv_splits, stream, &pages);
   }
@@ -964,7 +1053,7 @@ int msgl_paged_decode_attention_p16(const void* q, const void* k_cache, const vo
                              num_slots, static_cast<unsigned char*>(workspace) + op_ws,
                              static_cast<int*>(workspace), &kv_indptr, &kv_indices, &bound, stream);
   if (rc != MSGL_OK) return rc;
-  return decode_impl(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, nullptr, out, workspace,
+  return decode_impl(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_splits, gate, out, workspace,
                      op_ws, batch, num_q_heads, num_kv_heads, head_dim, num_slots, dtype, sm_scale,
                      max_kv_splits, stream);
 }
@@ -982,8 +1071,9 @@ size_t msgl_prefill_workspace_bytes_p16(int batch, int total_q, int64_t total_pa
 int msgl_paged_prefill_attention_p16(const void* q, const void* k_cache, const void* v_cache,
                                      const int32_t* qo_indptr, const int32_t* page_indptr,
                                      const int32_t* page_indices, const int32_t* kv_lens,
-                                     const int32_t* prefix_lens, void* out, void* workspace,
-                                     size_t workspace_bytes, int batch, int total_q, int num_q_heads,
+                                     const int32_t* prefix_lens, const void* gate, void* out,
+                                     void* workspace, size_t workspace_bytes, int batch, int total_q,
+                                     int num_q_heads,
                                      int num_kv_heads, int head_dim, int64_t num_slots, int dtype,
                                      float sm_scale, int max_len_extend, int is_cross_attention,
                                      int sliding_window_size, int page_size, int64_t total_pages,
@@ -1010,7 +1100,7 @@ int msgl_paged_prefill_attention_p16(const void* q, const void* k_cache, const v
     if (total_pages * page_size >= (1ll << 31))
       return fail(MSGL_BAD_SHAPE, std::string(op) + ": total_pages * page_size must be < 2^31");
     const PageIndex pages{page_indptr, page_indices, kv_lens, page_size};
-    return prefill_impl(q, k_cache, v_cache, qo_indptr, nullptr, nullptr, prefix_lens, nullptr, out,
+    return prefill_impl(q, k_cache, v_cache, qo_indptr, nullptr, nullptr, prefix_lens, gate, out,
                         workspace, op_ws, batch, total_q, total_pages * page_size, num_q_heads,
                         num_kv_heads, head_dim, num_slots, dtype, sm_scale, max_len_extend,
                         is_cross_attention, sliding_window_size, stream, &pages);
@@ -1021,7 +1111,7 @@ int msgl_paged_prefill_attention_p16(const void* q, const void* k_cache, const v
                              num_slots, static_cast<unsigned char*>(workspace) + op_ws,
                              static_cast<int*>(workspace), &kv_indptr, &kv_indices, &bound, stream);
   if (rc != MSGL_OK) return rc;
-  return prefill_impl(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens, nullptr, out,
+  return prefill_impl(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, prefix_lens, gate, out,
                       workspace, op_ws, batch, total_q, bound, num_q_heads, num_kv_heads, head_dim,
                       num_slots, dtype, sm_scale, max_len_extend, is_cross_attention,
                       sliding_window_size, stream);
@@ -1059,6 +1149,58 @@ int64_t msgl_fast_compare_key(const void* a, const void* b, int64_t len_a, int64
   }
   g_last_error = "fast_compare_key: Arrays must be int32 or int64.";
   return -1;
+}
+
+int msgl_build_attn_metadata(const int32_t* req, const int32_t* page_table, int64_t table_row_stride,
+                             int64_t table_rows, int64_t table_cols, int batch, int page_size,
+                             int split_chunk, int max_kv_splits, int64_t total_q, int64_t total_kv,
+                             int64_t total_pages, int32_t* qo_indptr, int32_t* kv_indptr,
+                             int32_t* prefix_lens, int32_t* num_kv_splits, int32_t* positions,
+                             int32_t* kv_indices, int32_t* page_indptr, int32_t* page_indices,
+                             void* status_word, void* stream) {
+  const char* op = "build_attn_metadata: ";
+  if (batch < 0 || table_rows < 0 || table_cols < 0 || table_row_stride < 0 || total_q < 0 ||
+      total_kv < 0 || total_pages < 0)
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "negative size");
+  if (page_size < 1 || max_kv_splits < 1 || split_chunk < 0)
+    return fail(MSGL_BAD_ARG, std::string(op) + "page_size and max_kv_splits must be >= 1, split_chunk >= 0");
+  if (batch > 65535) return fail(MSGL_BAD_SHAPE, std::string(op) + "batch must be <= 65535");
+  if (total_q >= (1ll << 31) || total_kv >= (1ll << 31))
+    return fail(MSGL_BAD_SHAPE, std::string(op) + "totals must be < 2^31");
+  if (batch == 0) return MSGL_OK;
+  if (!req || !page_table || !qo_indptr || !kv_indptr || !prefix_lens || !num_kv_splits ||
+      (total_q > 0 && !positions) || (page_indptr && total_pages > 0 && !page_indices))
+    return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  MetadataParams p{};
+  p.req = req;
+  p.page_table = page_table;
+  p.row_stride = table_row_stride;
+  p.table_rows = table_rows;
+  p.table_cols = table_cols;
+  p.batch = batch;
+  p.page_size = page_size;
+  p.split_chunk = split_chunk;
+  p.max_kv_splits = max_kv_splits;
+  p.total_q = total_q;
+  p.total_kv = total_kv;
+  p.total_pages = total_pages;
+  p.qo_indptr = qo_indptr;
+  p.kv_indptr = kv_indptr;
+  p.prefix_lens = prefix_lens;
+  p.num_kv_splits = num_kv_splits;
+  p.positions = positions;
+  p.kv_indices = kv_indices;
+  p.page_indptr = page_indptr;
+  p.page_indices = page_indptr ? page_indices : nullptr;
+  p.status = static_cast<int*>(status_word);
+  const int64_t avg = total_kv / batch + 1;
+  int bx = static_cast<int>((avg + 255) / 256);
+  if (bx > 32) bx = 32;
+  if (bx < 1) bx = 1;
+  build_metadata_kernel<<<dim3(bx, batch), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("build_attn_metadata", e);
+  return MSGL_OK;
 }
 
 int msgl_gather_kv_indices(const int32_t* page_table, int64_t table_row_stride,

@@ -25,6 +25,7 @@ __all__ = [
     "gather_kv_indices",
     "fast_compare_key",
     "qk_norm_rope_store",
+    "build_attn_metadata",
     "device_status",
 ]
 
@@ -187,7 +188,7 @@ def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indice
 
 def paged_decode_attention_p16(q, k_cache, v_cache, page_indptr, page_indices, kv_lens, num_kv_splits,
                                sm_scale: float, max_kv_splits: int, *, page_size: int = 16,
-                               stream=None) -> torch.Tensor:
+                               gate=None, stream=None) -> torch.Tensor:
     """``paged_decode_attention`` for a pool allocated in pages of ``page_size`` tokens
     (slot = page * page_size + offset): ``page_indptr`` ``(batch+1)``, ``page_indices``
     ``(total_pages)`` and the token lengths ``kv_lens`` ``(batch)`` replace the per-token
@@ -212,9 +213,12 @@ def paged_decode_attention_p16(q, k_cache, v_cache, page_indptr, page_indices, k
         need = ((lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits)) + 255) // 256 * 256
                 + lib.msgl_page_index_workspace_bytes(batch, total_pages, int(page_size)))
         ws = _workspace(need, q.device, sh, "decode")
+        if gate is not None:
+            _check_gate(op, gate, q)
         _lib.check(lib.msgl_paged_decode_attention_p16(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_indptr.data_ptr(),
-            page_indices.data_ptr(), kv_lens.data_ptr(), num_kv_splits.data_ptr(), out.data_ptr(),
+            page_indices.data_ptr(), kv_lens.data_ptr(), num_kv_splits.data_ptr(),
+            gate.data_ptr() if gate is not None else None, out.data_ptr(),
             ws.data_ptr(), ws.numel(), batch, hq, k_cache.shape[1], d, k_cache.shape[0],
             _DTYPES[q.dtype], float(sm_scale), int(max_kv_splits), int(page_size), total_pages, sh))
     return out
@@ -223,7 +227,7 @@ def paged_decode_attention_p16(q, k_cache, v_cache, page_indptr, page_indices, k
 def paged_prefill_attention_p16(q, k_cache, v_cache, qo_indptr, page_indptr, page_indices, kv_lens,
                                 prefix_lens, sm_scale: float, max_len_extend: int, *,
                                 page_size: int = 16, is_cross_attention: bool = False,
-                                sliding_window_size: int = 0, stream=None) -> torch.Tensor:
+                                sliding_window_size: int = 0, gate=None, stream=None) -> torch.Tensor:
     """``paged_prefill_attention`` with one id per page of ``page_size`` tokens instead of one
     per token; see ``paged_decode_attention_p16``."""
     op = "paged_prefill_attention_p16"
@@ -247,9 +251,12 @@ def paged_prefill_attention_p16(q, k_cache, v_cache, qo_indptr, page_indptr, pag
                                                     k_cache.shape[1], d, int(max_len_extend),
                                                     int(sliding_window_size))
         ws = _workspace(need, q.device, sh, "prefill")
+        if gate is not None:
+            _check_gate(op, gate, q)
         _lib.check(lib.msgl_paged_prefill_attention_p16(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
             page_indptr.data_ptr(), page_indices.data_ptr(), kv_lens.data_ptr(), prefix_lens.data_ptr(),
+            gate.data_ptr() if gate is not None else None,
             out.data_ptr(), ws.data_ptr(), ws.numel(), batch, total_q, hq, k_cache.shape[1], d,
             k_cache.shape[0], _DTYPES[q.dtype], float(sm_scale), int(max_len_extend),
             int(bool(is_cross_attention)), int(sliding_window_size), int(page_size), total_pages, sh))
@@ -365,6 +372,56 @@ def gather_kv_indices(page_table, table_idx, kv_indptr, total_kv: int, *, stream
             page_table.data_ptr(), page_table.stride(0), table_idx.contiguous().data_ptr(),
             kv_indptr.contiguous().data_ptr(), out.data_ptr(), batch, int(total_kv),
             page_table.shape[0], page_table.shape[1], status.data_ptr(), sh))
+    return out
+
+
+def build_attn_metadata(req_host: torch.Tensor, page_table: torch.Tensor, *, total_q: int, total_kv: int,
+                        page_size: int = 1, split_chunk: int = 0, max_kv_splits: int = 32,
+                        per_token_ids: bool = True, stream=None):
+    """Every index array of a step from the device page table with ONE host-to-device copy and
+    ONE launch.  ``req_host``: (3, batch) int32 on the host (pinned for a copy that does not
+    block): new tokens, KV lengths, page-table rows.  Returns a dict of int32 device views into
+    one buffer: ``qo_indptr``, ``kv_indptr``, ``prefix_lens``, ``num_kv_splits``, ``positions``,
+    ``kv_lens``, ``kv_indices`` (or None) and, with ``page_size`` > 1, ``page_indptr`` /
+    ``page_indices``.  Device-side form of AttnBackend.build_prefill_metadata /
+    build_decode_metadata (mini_sglang_mlx/attention/backend.py:205-307)."""
+    op = "build_attn_metadata"
+    _require(req_host.dim() == 2 and req_host.shape[0] == 3 and req_host.dtype == torch.int32
+             and not req_host.is_cuda and req_host.is_contiguous(),
+             f"{op}: req must be a contiguous (3, batch) int32 host tensor")
+    _require(page_table.dim() == 2 and page_table.dtype == torch.int32 and page_table.stride(1) == 1
+             and page_table.is_cuda, f"{op}: page_table must be a 2D int32 CUDA tensor with dense rows")
+    dev = page_table.device
+    batch = req_host.shape[1]
+    paged = int(page_size) > 1
+    total_pages = int((req_host[1].to(torch.int64) + page_size - 1).div(page_size, rounding_mode="floor").sum()) \
+        if paged else 0
+    sizes = dict(req=3 * batch, qo_indptr=batch + 1, kv_indptr=batch + 1, prefix_lens=batch,
+                 num_kv_splits=batch, positions=int(total_q),
+                 kv_indices=int(total_kv) if per_token_ids else 0,
+                 page_indptr=batch + 1 if paged else 0, page_indices=total_pages)
+    sh = _stream_handle(stream, dev)
+    with torch.cuda.device(dev), torch.cuda.stream(torch.cuda.ExternalStream(sh, device=dev)):
+        buf = torch.empty(sum(sizes.values()), dtype=torch.int32, device=dev)
+        out, off = {}, 0
+        for name, n in sizes.items():
+            out[name] = buf[off:off + n]
+            off += n
+        out["req"].copy_(req_host.view(-1), non_blocking=True)
+        status = _workspace(256, dev, sh, "decode")
+        ptr = lambda name: out[name].data_ptr() if sizes[name] else None  # noqa: E731
+        _lib.check(_lib.lib().msgl_build_attn_metadata(
+            out["req"].data_ptr(), page_table.data_ptr(), page_table.stride(0), page_table.shape[0],
+            page_table.shape[1], batch, int(page_size), int(split_chunk), int(max_kv_splits),
+            int(total_q), int(total_kv), total_pages, out["qo_indptr"].data_ptr(),
+            out["kv_indptr"].data_ptr(), out["prefix_lens"].data_ptr(), out["num_kv_splits"].data_ptr(),
+            ptr("positions"), ptr("kv_indices"), ptr("page_indptr"), ptr("page_indices"),
+            status.data_ptr(), sh))
+    out["kv_lens"] = out["req"][batch:2 * batch]
+    if not per_token_ids:
+        out["kv_indices"] = None
+    if not paged:
+        out["page_indptr"] = out["page_indices"] = None
     return out
 
 

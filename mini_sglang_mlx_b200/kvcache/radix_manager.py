@@ -12,6 +12,13 @@ without a host round trip.  The edge comparison is ``fast_compare_key``.
 Recency is a logical clock (one tick per walk), which keeps eviction order
 deterministic.  The hybrid (recurrent-state) variant of the reference is not
 built: it belongs to a model family outside the attention path.
+
+``page_size`` > 1 (the reference hard-wires 1, mini_sglang_mlx/engine/engine.py:103) keeps the
+tree page-aligned so that the page-granular attention entries can use what it returns: every
+edge holds whole pages, an edge is split only at a page boundary (a match that ends inside a
+page is rounded down: that page is recomputed, not shared), only the whole pages of a finished
+request are inserted, and children are told apart by their first PAGE of tokens (two edges
+may agree on their first token and differ later in the page).
 """
 from __future__ import annotations
 
@@ -50,9 +57,9 @@ class RadixTreeNode:
     def is_leaf(self) -> bool:
         return not self.children
 
-    def attach(self, parent: "RadixTreeNode") -> None:
+    def attach(self, parent: "RadixTreeNode", page_size: int = 1) -> None:
         self.parent = parent
-        parent.children[int(self.key[0])] = self
+        parent.children[_child_key(self.key, 0, page_size)] = self
 
     def __lt__(self, other: "RadixTreeNode") -> bool:  # heap order: least recently used first
         return (self.timestamp, self.uid) < (other.timestamp, other.uid)
@@ -63,6 +70,13 @@ class RadixCacheHandle(BaseCacheHandle):
     node: RadixTreeNode
 
 
+def _child_key(key: np.ndarray, pos: int, page_size: int):
+    """What a node's children are indexed by: the first token of the edge, or its first page."""
+    if page_size == 1:
+        return int(key[pos])
+    return key[pos:pos + page_size].tobytes()
+
+
 def _as_key(input_ids) -> np.ndarray:
     if isinstance(input_ids, torch.Tensor):
         input_ids = input_ids.detach().cpu().numpy()
@@ -70,7 +84,9 @@ def _as_key(input_ids) -> np.ndarray:
 
 
 class RadixCacheManager:
-    def __init__(self, device=None) -> None:
+    def __init__(self, device=None, page_size: int = 1) -> None:
+        assert page_size >= 1
+        self.page_size = page_size
         self.device = torch.device(device) if device is not None else torch.device("cpu")
         self.empty_tensor = torch.zeros(0, dtype=torch.int32, device=self.device)
         self._clock = itertools.count(1)
@@ -80,8 +96,11 @@ class RadixCacheManager:
         self.protected_size = 0
 
     # ------------------------------------------------------------------ queries
+    def _whole_pages(self, key: np.ndarray) -> np.ndarray:
+        return key if self.page_size == 1 else key[: key.shape[0] // self.page_size * self.page_size]
+
     def match_prefix(self, input_ids) -> Tuple[RadixCacheHandle, torch.Tensor]:
-        node, matched = self._walk(_as_key(input_ids))
+        node, matched = self._walk(self._whole_pages(_as_key(input_ids)))
         if matched == 0:
             return RadixCacheHandle(0, self.root_node), self.empty_tensor
         parts: List[torch.Tensor] = []
@@ -117,12 +136,14 @@ class RadixCacheManager:
     def insert_prefix(self, input_ids, indices: torch.Tensor) -> int:
         key = _as_key(input_ids)
         assert indices.shape[0] == key.shape[0], "one slot id per token"
+        key = self._whole_pages(key)          # a trailing partial page is not cached
         node, matched = self._walk(key)
         if matched < key.shape[0]:
             leaf = RadixTreeNode(next(self._clock))
             leaf.key = key[matched:].copy()
-            leaf.value = indices[matched:].to(device=self.device, dtype=torch.int32).reshape(-1).clone()
-            leaf.attach(node)
+            leaf.value = indices[matched:key.shape[0]].to(device=self.device,
+                                                          dtype=torch.int32).reshape(-1).clone()
+            leaf.attach(node, self.page_size)
             self.evictable_size += leaf.length
         return matched
 
@@ -142,7 +163,7 @@ class RadixCacheManager:
             freed.append(node.value)
             self.evictable_size -= node.length
             parent = node.parent
-            del parent.children[int(node.key[0])]
+            del parent.children[_child_key(node.key, 0, self.page_size)]
             if parent.is_leaf() and parent.ref_count == 0 and not parent.is_root():
                 heapq.heappush(heap, parent)
         return torch.cat(freed)
@@ -156,7 +177,8 @@ class RadixCacheManager:
             if node.is_root():
                 continue
             assert node.length > 0 and node.value.shape[0] == node.length
-            assert node.parent.children.get(int(node.key[0])) is node
+            assert node.length % self.page_size == 0, "an edge that does not hold whole pages"
+            assert node.parent.children.get(_child_key(node.key, 0, self.page_size)) is node
             assert all(c.ref_count <= node.ref_count for c in node.children.values()), \
                 "a locked node below an unlocked one"
             if node.ref_count == 0:
@@ -182,9 +204,9 @@ class RadixCacheManager:
         upper = RadixTreeNode(node.timestamp)
         upper.key, upper.value = node.key[:pos].copy(), node.value[:pos]
         upper.ref_count = node.ref_count
-        upper.attach(node.parent)
+        upper.attach(node.parent, self.page_size)
         node.key, node.value = node.key[pos:].copy(), node.value[pos:]
-        node.attach(upper)
+        node.attach(upper, self.page_size)
         return upper
 
     def _walk(self, key: np.ndarray) -> Tuple[RadixTreeNode, int]:
@@ -192,14 +214,15 @@ class RadixCacheManager:
         and the number of tokens matched; refreshes the recency of fully matched nodes."""
         tick = next(self._clock)
         node, matched, n = self.root_node, 0, key.shape[0]
-        while matched < n:
-            child = node.children.get(int(key[matched]))
+        ps = self.page_size
+        while matched + ps <= n:
+            child = node.children.get(_child_key(key, matched, ps))
             if child is None:
                 break
-            m = fast_compare_key(child.key, key[matched:])
+            m = fast_compare_key(child.key, key[matched:]) // ps * ps   # whole pages only
             matched += m
             if m < child.length:
-                return self._split(child, m), matched
+                return self._split(child, m), matched    # m >= ps: the first page is the child key
             child.timestamp = tick
             node = child
         return node, matched

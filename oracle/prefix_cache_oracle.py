@@ -16,25 +16,32 @@ from typing import Dict, List, Sequence, Tuple
 
 
 class PrefixCacheModel:
-    def __init__(self) -> None:
-        self.slot_of: Dict[Tuple[int, ...], int] = {}   # prefix -> slot of its last token
+    """``page_size`` > 1 is the page-aligned variant of this build (the reference has one token
+    per page): a prefix is cached, matched and shared in whole pages only, so the model keeps one
+    entry per cached prefix of whole pages."""
+
+    def __init__(self, page_size: int = 1) -> None:
+        self.page_size = page_size
+        self.slots_of: Dict[Tuple[int, ...], List[int]] = {}   # prefix -> slots of its last page
 
     def match(self, tokens: Sequence[int]) -> List[int]:
         out: List[int] = []
-        for i in range(len(tokens)):
-            slot = self.slot_of.get(tuple(tokens[: i + 1]))
-            if slot is None:
+        ps = self.page_size
+        for end in range(ps, len(tokens) + 1, ps):
+            slots = self.slots_of.get(tuple(tokens[:end]))
+            if slots is None:
                 break
-            out.append(slot)
+            out.extend(slots)
         return out
 
     def insert(self, tokens: Sequence[int], slots: Sequence[int]) -> int:
         """Returns how many leading tokens were cached already (their slots are kept)."""
+        ps = self.page_size
         already = len(self.match(tokens))
-        for i in range(already, len(tokens)):
-            self.slot_of[tuple(tokens[: i + 1])] = int(slots[i])
+        for end in range(already + ps, len(tokens) + 1, ps):
+            self.slots_of[tuple(tokens[:end])] = [int(x) for x in slots[end - ps:end]]
         return already
 
     @property
     def size(self) -> int:
-        return len(self.slot_of)
+        return len(self.slots_of) * self.page_size

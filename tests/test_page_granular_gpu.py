@@ -126,7 +126,8 @@ def test_workspace_size_is_checked_through_the_c_abi():
     ws = torch.zeros(1024, dtype=torch.uint8, device="cuda")
     rc = lib.msgl_paged_decode_attention_p16(
         q.data_ptr(), kc.data_ptr(), kc.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
-        q.data_ptr(), ws.data_ptr(), ws.numel(), 3, 4, 2, 128, 1600, _lib.DTYPE_BF16, 0.1, 32, 16, 100, 0)
+        None, q.data_ptr(), ws.data_ptr(), ws.numel(), 3, 4, 2, 128, 1600, _lib.DTYPE_BF16, 0.1, 32, 16,
+        100, 0)
     assert rc != 0 and "workspace too small" in lib.msgl_last_error_string().decode()
 
 

@@ -27,7 +27,10 @@ class _Prompt:
         self.input_len = len(tokens)
 
 
-def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result():
+@pytest.mark.parametrize("page_size", [1, 16])
+def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result(page_size):
+    """page_size 16: page-granular allocation, page-aligned prefix tree, attention through the
+    page-granular operators; a match ends on a page boundary, the rest is recomputed."""
     from mini_sglang_mlx_b200.attention import AttnBackend
     from mini_sglang_mlx_b200.core import Batch, BatchPhase, Req
     from mini_sglang_mlx_b200.kvcache import MHAKVCache
@@ -39,12 +42,13 @@ def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result():
     emb_k = torch.randn(VOCAB, HKV, D, generator=g).bfloat16()
     emb_v = torch.randn(VOCAB, HKV, D, generator=g).bfloat16()
 
-    num_pages, max_reqs, max_len = 1024, 4, 512
-    pool = MHAKVCache(HKV, 1, D, num_pages + 1, torch.bfloat16)
+    ps = page_size
+    num_pages, max_reqs, max_len = 1024 // ps * (4 if ps > 1 else 1), 4, 512
+    pool = MHAKVCache(HKV, 1, D, num_pages * ps + 1, torch.bfloat16)
     page_table = torch.zeros((max_reqs + 1, max_len), dtype=torch.int32, device=dev)
     tm = TableManager(max_reqs, page_table)
-    cm = CacheManager(dev, num_pages)
-    be = AttnBackend(_Cfg, pool, page_table)
+    cm = CacheManager(dev, num_pages, page_size=ps)
+    be = AttnBackend(_Cfg, pool, page_table, page_size=ps)
 
     rng = np.random.default_rng(3)
     shared = rng.integers(0, VOCAB, size=300).tolist()
@@ -52,7 +56,7 @@ def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result():
                shared[:150] + rng.integers(0, VOCAB, size=60).tolist(),     # splits the first edge at 150
                shared[:200] + rng.integers(0, VOCAB, size=1).tolist(),      # one new token
                shared[:150] + rng.integers(0, VOCAB, size=333).tolist()]    # long suffix
-    expect_cached = [0, 150, 200, 150]
+    expect_cached = [w // ps * ps for w in [0, 150, 200, 150]]
 
     for tokens, want in zip(prompts, expect_cached):
         handle, cached = cm.match_req(_Prompt(tokens))
@@ -61,7 +65,7 @@ def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result():
         row = tm.allocate()
         n = len(tokens)
         page_table[row, :want] = cached
-        fresh = cm.allocate(n - want)
+        fresh = cm.allocate(n - want, start=want)
         page_table[row, want:n] = fresh
         req = Req(table_idx=row, cached_len=want, device_len=n)
         batch = Batch(reqs=[req], phase=BatchPhase.PREFILL, out_loc=fresh)
@@ -81,6 +85,6 @@ def test_a_cached_prefix_is_reused_and_gives_the_full_prefill_result():
         tm.free(row)
         cm.check_integrity()
 
-    # the pool holds every distinct prefix once
-    distinct = {tuple(p[: i + 1]) for p in prompts for i in range(len(p))}
-    assert cm.manager.size_info.total_size == len(distinct)
+    # the pool holds every distinct prefix (of whole pages) once
+    distinct = {tuple(p[: i + 1]) for p in prompts for i in range(len(p)) if (i + 1) % ps == 0}
+    assert cm.manager.size_info.total_size == len(distinct) * ps

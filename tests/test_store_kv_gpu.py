@@ -229,3 +229,83 @@ def test_ops_on_a_stream_that_is_not_the_current_one():
     assert_close_to_oracle(outp, O.paged_prefill_attention_oracle(qp, kc, vc, qo, indptr, slots, pre,
                                                                   1 / math.sqrt(d)),
                            "prefill (key range split) on a side stream")
+
+
+def test_page_granular_metadata_and_attention_through_the_backend():
+    """A backend over page-structured slots (pages of 16 tokens): the metadata carries one id per
+    page, attention runs through the page-granular operators, and prefill + decode steps match the
+    oracle over the per-token view of the same table."""
+    from mini_sglang_mlx_b200.attention import AttnBackend
+    from mini_sglang_mlx_b200.core import Batch, BatchPhase, Req
+    from mini_sglang_mlx_b200.kvcache import MHAKVCache
+    from mini_sglang_mlx_b200.kernel import device_status
+    ps, num_pages, rows, max_seq = 16, 512, 4, 1024
+    pool = MHAKVCache(_Cfg.num_kv_heads, 1, _Cfg.head_dim, num_pages * ps, torch.bfloat16)
+    g = torch.Generator().manual_seed(2)
+    pages = torch.randperm(num_pages, generator=g)[: rows * (max_seq // ps)].view(rows, max_seq // ps)
+    table = (pages[:, :, None] * ps + torch.arange(ps)[None, None]).reshape(rows, max_seq).int().cuda()
+    be = AttnBackend(_Cfg, pool, table, page_size=ps)
+    reqs = [Req(table_idx=2, cached_len=0, device_len=100), Req(table_idx=0, cached_len=0, device_len=33),
+            Req(table_idx=3, cached_len=0, device_len=512)]
+    device_status()
+    md = be.build_prefill_metadata(reqs)
+    need = [(r.device_len + ps - 1) // ps for r in reqs]
+    assert md.kv_indices is None and md.page_size == ps
+    assert md.page_indptr.tolist() == [0, need[0], need[0] + need[1], sum(need)]
+    assert md.kv_lens.tolist() == [r.device_len for r in reqs]
+    want = torch.cat([pages[r.table_idx, :n] for r, n in zip(reqs, need)])
+    assert md.page_indices.cpu().tolist() == want.tolist()
+    assert md.qo_indptr.tolist() == [0, 100, 133, 645] and md.prefix_lens.tolist() == [0, 0, 0]
+    assert md.positions.cpu().tolist() == sum((list(range(r.device_len)) for r in reqs), [])
+    assert device_status() == 0
+
+    scale = 1 / math.sqrt(_Cfg.head_dim)
+    n = sum(r.extend_len for r in reqs)
+    q = torch.randn(n, _Cfg.num_qo_heads, _Cfg.head_dim, generator=g).bfloat16().cuda()
+    k = torch.randn(n, _Cfg.num_kv_heads, _Cfg.head_dim, generator=g).bfloat16().cuda()
+    v = torch.randn(n, _Cfg.num_kv_heads, _Cfg.head_dim, generator=g).bfloat16().cuda()
+    out_loc = torch.cat([table[r.table_idx, r.cached_len:r.device_len] for r in reqs])
+    batch = Batch(reqs=reqs, phase=BatchPhase.PREFILL, out_loc=out_loc)
+    be.prepare_metadata(batch)
+    out = be.forward(q, k, v, 0, batch)
+    kv_lens = [r.device_len for r in reqs]
+    slots = torch.cat([table[r.table_idx, : r.device_len] for r in reqs])
+    ref = O.paged_prefill_attention_oracle(q, pool.k_cache(0), pool.v_cache(0), md.qo_indptr,
+                                           torch.from_numpy(O.build_indptr(kv_lens)), slots,
+                                           md.prefix_lens, scale)
+    assert_close_to_oracle(out, ref, "prefill through the page-granular backend")
+    for _ in range(2):                         # decode steps: one token more per request
+        for r in reqs:
+            r.complete_one()
+        qd = torch.randn(len(reqs), _Cfg.num_qo_heads, _Cfg.head_dim, generator=g).bfloat16().cuda()
+        kd = torch.randn(len(reqs), _Cfg.num_kv_heads, _Cfg.head_dim, generator=g).bfloat16().cuda()
+        vd = torch.randn(len(reqs), _Cfg.num_kv_heads, _Cfg.head_dim, generator=g).bfloat16().cuda()
+        out_loc = torch.stack([table[r.table_idx, r.cached_len] for r in reqs])
+        batch = Batch(reqs=reqs, phase=BatchPhase.DECODE, out_loc=out_loc)
+        be.prepare_metadata(batch)
+        assert batch.attn_metadata.positions.tolist() == [r.cached_len for r in reqs]
+        outd = be.forward(qd, kd, vd, 0, batch)
+        kv_lens = [r.device_len for r in reqs]
+        slots = torch.cat([table[r.table_idx, : r.device_len] for r in reqs])
+        refd = O.paged_decode_attention_oracle(qd, pool.k_cache(0), pool.v_cache(0),
+                                               torch.from_numpy(O.build_indptr(kv_lens)), slots, scale)
+        assert_close_to_oracle(outd, refd, "decode through the page-granular backend")
+    assert device_status() == 0
+
+
+def test_metadata_kernel_reports_rows_and_lengths_outside_the_table():
+    from mini_sglang_mlx_b200.kernel import build_attn_metadata, device_status
+    table = torch.arange(4 * 64, dtype=torch.int32).view(4, 64).cuda()
+    device_status()
+    ok = build_attn_metadata(torch.tensor([[3, 1], [10, 40], [1, 3]], dtype=torch.int32), table,
+                             total_q=4, total_kv=50)
+    assert device_status() == 0
+    assert ok["kv_indptr"].tolist() == [0, 10, 50] and ok["qo_indptr"].tolist() == [0, 3, 4]
+    assert ok["kv_indices"].tolist() == list(range(64, 74)) + list(range(192, 232))
+    assert ok["positions"].tolist() == [7, 8, 9, 39] and ok["prefix_lens"].tolist() == [7, 39]
+    assert ok["num_kv_splits"].tolist() == [1, 1]
+    for bad in ([[3, 1], [10, 40], [1, 9]],          # a table row that does not exist
+                [[3, 1], [10, 80], [1, 3]],          # longer than a table row
+                [[30, 1], [10, 40], [1, 3]]):        # more new tokens than tokens
+        build_attn_metadata(torch.tensor(bad, dtype=torch.int32), table, total_q=64, total_kv=128)
+        assert device_status() == 2
