@@ -45,10 +45,25 @@ import torch  # noqa: E402
 METRIC = "paged decode HBM GB/s + prefill TFLOP/s vs roofline at 1/2/4/8 B200"
 L2_FLUSH_BYTES = 256 << 20
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes per launch of the dominant kernel divided by the workload's algorithmic bytes, from
-# the ncu captures summarised under profiles/ (decode: captured at batch 16 and scaled by the
-# tokens read; prefill: K/V are re-read from L2, not DRAM, across query tiles and heads).
-TRAFFIC_PER_ALGORITHMIC_BYTE = {"decode": 1.004, "prefill": 0.81}
+# DRAM bytes per launch of the dominant kernel divided by the workload's algorithmic bytes, each
+# from an ncu capture of that workload summarised under profiles/ (cfg4 and cfg5a were captured at a
+# reduced batch and scale with the tokens read).  A workload without a capture reports no traffic.
+TRAFFIC_PER_ALGORITHMIC_BYTE = {
+    "cfg1": (1.00, "profiles/dram_traffic_cfg1_cfg3.md"),
+    "cfg2": (0.83, "profiles/prefill_tc_kernel_cfg2.md"),
+    "cfg3": (1.03, "profiles/dram_traffic_cfg1_cfg3.md"),
+    "cfg4": (1.02, "profiles/prefill_tc_kernel_cfg4_batch8.md"),
+    "cfg5a": (1.005, "profiles/decode_partial_kernel_cfg5a_batch16.md"),
+}
+
+
+def traffic_of(w):
+    """(bytes per launch, source) from the capture of this workload, or (None, None)."""
+    key = w.name.split("_")[0]
+    if key not in TRAFFIC_PER_ALGORITHMIC_BYTE or INDEX != "page":
+        return None, None
+    ratio, source = TRAFFIC_PER_ALGORITHMIC_BYTE[key]
+    return ratio * w.algorithmic_bytes(), source
 
 
 def load_peaks():
@@ -138,8 +153,9 @@ def _make_workload(name: str, device, rank: int):
     if name == "cfg1":
         from mini_sglang_mlx_b200.attention import compute_num_kv_splits
         w = S.cfg1_decode(seed=101 + seed_shift, device=device, **kw)
-        w.num_kv_splits = torch.tensor(compute_num_kv_splits(w.kv_lens, w.hkv), dtype=torch.int32,
-                                       device=device)
+        splits = compute_num_kv_splits(w.kv_lens, w.hkv)
+        w.num_kv_splits = torch.tensor(splits, dtype=torch.int32, device=device)
+        w.max_kv_splits = max(splits)      # the launch grid: no more split slots than any sequence uses
         return w
     if name == "cfg2":
         return S.cfg2_prefill(seed=202 + seed_shift, device=device, **kw)
@@ -152,6 +168,7 @@ def _make_workload(name: str, device, rank: int):
         w = S.cfg5a_decode(seed=505 + seed_shift, device=device, **kw)
         splits = compute_num_kv_splits(w.kv_lens, w.hkv)
         w.num_kv_splits = torch.tensor(splits, dtype=torch.int32, device=device)
+        w.max_kv_splits = max(splits)
         return w
     if name.startswith("cfg5b"):
         _, c, p = name.split("_")
@@ -180,14 +197,9 @@ def run_op(w):
 
 
 def launches_per_step(w) -> int:
-    from mini_sglang_mlx_b200 import _lib
-    if w.kind == "decode":
-        return 2
-    total_kv = w.page_indices.numel() * 16 if w.index == "page" else w.kv_indices.numel()
-    need = _lib.lib().msgl_prefill_workspace_bytes(w.batch, w.q.shape[0], total_kv, w.hq,
-                                                   w.hkv, w.head_dim, w.max_len_extend,
-                                                   w.sliding_window_size)
-    return 2 if need > 256 else 1
+    """Kernels of this library per operator call: one.  The key-range splits of the decode kernel
+    and of the prefill kernel are merged by the CTA that finishes last, inside the same launch."""
+    return 1
 
 
 def barrier(dist_on: bool):
@@ -559,15 +571,13 @@ def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, pea
         peak = peaks["bf16_tflops"]
         ach = w.algorithmic_flops() / step_s / 1e12
         roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                "frac": ach / peak,
-                "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE["prefill"] * w.algorithmic_bytes(),
+                "frac": ach / peak, "traffic": traffic_of(w)[0], "traffic_source": traffic_of(w)[1],
                 "peak_source": f"{peak_kind} burst bf16"}
     else:
         peak = peaks["hbm_gbs"]
         ach = w.algorithmic_bytes() / step_s / 1e9
         roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                "traffic": (TRAFFIC_PER_ALGORITHMIC_BYTE["decode"] * w.algorithmic_bytes()
-                            if w.kind == "decode" else None),
+                "traffic": traffic_of(w)[0], "traffic_source": traffic_of(w)[1],
                 "peak_source": f"{peak_kind} copy bandwidth",
                 "flop_per_byte": intensity, "ridge_flop_per_byte": ridge}
     res = {"workload": w.name, "value": value, "unit": unit, "ms_per_step": total_ms / steps,

@@ -84,27 +84,32 @@ def compute_num_kv_splits(kv_lens: Sequence[int], num_kv_heads: int, *, sm_count
     """Per-sequence split count of the decode op.
 
     ``reference``: ``min(max, max(1, ceil(L/128)))`` (reference lines 304-307).
-    ``b200``: one split per ``chunk`` tokens where ``chunk`` spreads the batch's
-    ``sum(L) * num_kv_heads`` token-heads over about 16 CTAs per SM, clamped to
-    [256, 4096] tokens: enough CTAs to fill the SMs at small batch, small
-    enough CTAs that a long sequence does not leave a tail.
+    ``b200``: one split per ``chunk`` tokens (``split_chunk_tokens``).
     """
     if policy == "reference":
         return [min(max_kv_splits, max(1, (l + 127) // 128)) for l in kv_lens]
-    total = sum(kv_lens) * num_kv_heads
-    chunk = -(-total // (sm_count * 16))
-    chunk = min(4096, max(256, chunk))
-    chunk = -(-chunk // 64) * 64
+    chunk = split_chunk_tokens(sum(kv_lens), num_kv_heads, sm_count=sm_count, batch=len(kv_lens))
     return [min(max_kv_splits, max(1, -(-l // chunk))) for l in kv_lens]
 
 
-def split_chunk_tokens(total_kv: int, num_kv_heads: int, *, sm_count: int = 148,
+def split_chunk_tokens(total_kv: int, num_kv_heads: int, *, sm_count: int = 148, batch: int = 0,
                        policy: str = "b200") -> int:
-    """Tokens per split of ``compute_num_kv_splits`` for a batch with ``total_kv`` KV tokens."""
+    """Tokens per split of the decode op for a batch with ``total_kv`` KV tokens.
+
+    ``b200``: the batch's ``total_kv * num_kv_heads`` token-heads spread over about 16 CTAs per
+    SM, clamped to [256, 4096] tokens: enough CTAs to fill the SMs, small enough that a long
+    sequence does not leave a tail.  A small batch that would then need a little more than one
+    wave of CTAs (two are resident per SM) gets the chunk that makes it exactly one: a CTA of
+    such a batch is a chain of memory latencies, and a second, partial wave doubles it."""
     if policy == "reference":
         return 128
     chunk = -(-total_kv * num_kv_heads // (sm_count * 16))
     chunk = min(4096, max(256, chunk))
+    slots = 2 * sm_count
+    ctas = (total_kv // chunk + batch) * num_kv_heads          # upper bound with this chunk
+    room = slots // num_kv_heads - batch                        # split slots per head in one wave
+    if batch > 0 and room > 0 and slots < ctas <= 2 * slots:
+        chunk = min(4096, max(chunk, -(-total_kv // room)))
     return -(-chunk // 64) * 64
 
 
@@ -260,10 +265,19 @@ class AttnBackend:
             with torch.cuda.device(self.page_table.device):
                 self._sm_count = max(1, _lib.lib().msgl_device_sm_count())
         chunk = split_chunk_tokens(sum(kv_lens), self.config.num_kv_heads, sm_count=self._sm_count,
-                                   policy=self.split_policy)
-        md = self._index_arrays(reqs, [1] * len(reqs), kv_lens, chunk)
-        return DecodeMetadata(positions=md["positions"] if positions is None else positions,
+                                   batch=len(kv_lens), policy=self.split_policy)
+        # "new tokens" of a decode row = everything behind what the request has cached, so that
+        # the kernel's prefix_lens are the reference's positions (req.cached_len, line 276)
+        extend = [max(1, min(kv_lens[i], kv_lens[i] - reqs[i].cached_len)) for i in range(len(reqs))]
+        md = self._index_arrays(reqs, extend, kv_lens, chunk)
+        # the split dimension of the launch grid: what the longest sequence needs, not the cap
+        # (CTAs of split slots no sequence uses would only start, look up a length and leave)
+        # (the reference policy keeps the reference's constant, backend.py:293)
+        max_splits = MAX_KV_SPLITS
+        if self.split_policy != "reference" and kv_lens:
+            max_splits = min(MAX_KV_SPLITS, max(1, -(-max(kv_lens) // chunk)))
+        return DecodeMetadata(positions=md["prefix_lens"] if positions is None else positions,
                               kv_indptr=md["kv_indptr"], kv_indices=md["kv_indices"],
-                              num_kv_splits=md["num_kv_splits"], max_kv_splits=MAX_KV_SPLITS,
+                              num_kv_splits=md["num_kv_splits"], max_kv_splits=max_splits,
                               page_indptr=md["page_indptr"], page_indices=md["page_indices"],
                               kv_lens=md["kv_lens"], page_size=self.page_size if self._paged_ops else 1)

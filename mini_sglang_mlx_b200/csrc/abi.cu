@@ -197,6 +197,7 @@ struct PrefillPlan {
   size_t part_o_bytes, part_ml_bytes, plan_bytes;
 };
 
+
 // Query blocks that fill at most one 128-row sub-tile (verify, draft blocks) run the
 // one-sub-tile shape (64-token key tiles, two CTAs per SM); longer chunks the two-sub-tile
 // shape with 128-token key tiles.  head_dim 256 always runs the one-sub-tile shape (its

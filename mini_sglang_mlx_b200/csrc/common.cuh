@@ -154,12 +154,39 @@ __device__ __forceinline__ float quad_sum(float v) {
   return v;
 }
 
+// Development aid, compiled in only with -DMSGL_TRACE: one record per CTA (SM, wall-clock entry
+// and exit, cycle counts at the milestones of softmax group 0) read back through
+// msgl_debug_read_cta_trace.
+#ifdef MSGL_TRACE
+constexpr int kTraceCtas = 8192;
+__device__ long long g_cta_trace[kTraceCtas][32];
+__device__ __forceinline__ long long trace_wall() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int trace_smid() {
+  int s;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(s));
+  return s;
+}
+#define MSGL_TR(slot, value)                                                   \
+  do {                                                                         \
+    if (blockIdx.x < kTraceCtas) g_cta_trace[blockIdx.x][slot] = (value);      \
+  } while (0)
+#else
+#define MSGL_TR(slot, value) do { } while (0)
+#endif
+
 // ---------------------------------------------------------------- mbarrier / TMA
 constexpr long long kTcWaitCycles = 4000000000LL;            // bound of every barrier wait (~2 s)
 constexpr int kTmaBoxRows = 16;   // token rows of one TMA box (= the smallest page)
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");

@@ -99,26 +99,20 @@ __global__ void __launch_bounds__(NWARPS * 32)
   const int b = blockIdx.z;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  const int kv_begin = PAGED ? p.page_indptr[b] : p.kv_indptr[b];   // pages / tokens
-  const int L = decode_seq_len(p, b);
-  if (PAGED && split == 0 && h == 0 && threadIdx.x == 0 && p.status) {
-    const int len = p.kv_lens[b];   // negative or beyond the sequence's pages: clamped, reported
-    if (len < 0 || len > L) atomicExch(p.status, 2);
-  }
-  const int splits = decode_effective_splits(L, p.num_kv_splits, b, p.max_splits, CTA_TOKENS);
-  if (split >= splits) return;
-  const int per = ceil_div(ceil_div(L, splits), CTA_TOKENS) * CTA_TOKENS;
-  const int t_begin = split * per;
-  const int t_end = min(L, t_begin + per);
+#ifdef MSGL_TRACE
+  const int tr_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+#define MSGL_TRD(slot, value) do { if (threadIdx.x == 0 && tr_id < kTraceCtas) g_cta_trace[tr_id][slot] = (value); } while (0)
+  MSGL_TRD(0, trace_wall());
+  MSGL_TRD(1, clock64());
+  MSGL_TRD(2, trace_smid());
+  MSGL_TRD(10, 0);
+#else
+#define MSGL_TRD(slot, value) do { } while (0)
+#endif
 
   const int G = p.group;
   const T* __restrict__ q = static_cast<const T*>(p.q);
-  const unsigned char* __restrict__ kbase = static_cast<const unsigned char*>(p.k_cache);
-  const unsigned char* __restrict__ vbase = static_cast<const unsigned char*>(p.v_cache);
-  const int64_t slot_stride = static_cast<int64_t>(p.hkv) * ROW_BYTES;
-  const int64_t head_off = static_cast<int64_t>(h) * ROW_BYTES;
-
+  // (issued before the sequence's length is looked up: the two round trips to memory overlap)
   // ---- Q fragments: rows = query heads of this KV head (rows >= G are zero)
   uint32_t qf[KSTEPS][4];
   {
@@ -138,6 +132,24 @@ __global__ void __launch_bounds__(NWARPS * 32)
       qf[ks][3] = v1 ? q1[w + 4] : 0u;
     }
   }
+
+  const int kv_begin = PAGED ? p.page_indptr[b] : p.kv_indptr[b];   // pages / tokens
+  const int L = decode_seq_len(p, b);
+  if (PAGED && split == 0 && h == 0 && threadIdx.x == 0 && p.status) {
+    const int len = p.kv_lens[b];   // negative or beyond the sequence's pages: clamped, reported
+    if (len < 0 || len > L) atomicExch(p.status, 2);
+  }
+  const int splits = decode_effective_splits(L, p.num_kv_splits, b, p.max_splits, CTA_TOKENS);
+  if (split >= splits) return;
+  MSGL_TRD(3, clock64());      // lengths known
+  const int per = ceil_div(ceil_div(L, splits), CTA_TOKENS) * CTA_TOKENS;
+  const int t_begin = split * per;
+  const int t_end = min(L, t_begin + per);
+
+  const unsigned char* __restrict__ kbase = static_cast<const unsigned char*>(p.k_cache);
+  const unsigned char* __restrict__ vbase = static_cast<const unsigned char*>(p.v_cache);
+  const int64_t slot_stride = static_cast<int64_t>(p.hkv) * ROW_BYTES;
+  const int64_t head_off = static_cast<int64_t>(h) * ROW_BYTES;
 
   // ---- warp-private ring of K/V group tiles
   // PAGED: tiles are TMA destinations with the 128-byte swizzle, which is a function of the
@@ -280,8 +292,10 @@ __global__ void __launch_bounds__(NWARPS * 32)
     }
   }
 
+  MSGL_TRD(4, clock64());      // Q in registers, first copies issued
   bool alive = true;
   for (int step = 0; step < nsteps; ++step) {
+    if (step == 1) MSGL_TRD(5, clock64());   // first group consumed
     if constexpr (PAGED) {
       // bounded wait for this step's stage
       const uint32_t bar = bar_of(step % NSTAGES);
@@ -379,6 +393,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
       }
     }
   }
+  MSGL_TRD(6, clock64());      // main loop done
   cp_async_wait<0>();
   if (PAGED && !alive && p.status && lane == 0) atomicExch(p.status, 1);   // a wait ran out
   l0 = quad_sum(l0);
@@ -439,6 +454,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
           den > 0.f ? M * kLn2 + __logf(den) : -INFINITY;
     }
   }
+  MSGL_TRD(7, clock64());      // partial (or final rows) written
+  MSGL_TRD(10, trace_wall());
   if (splits == 1) return;
 
   // ---- the split that arrives last merges: out = sum_s e^(lse_s - M) O_s / sum_s e^(lse_s - M)
@@ -453,6 +470,9 @@ __global__ void __launch_bounds__(NWARPS * 32)
     if (s_last) *ticket = 0;
   }
   __syncthreads();
+  MSGL_TRD(8, clock64());      // arrival counted
+  MSGL_TRD(10, trace_wall());
+  MSGL_TRD(11, s_last);
   if (s_last == 0) return;
   __threadfence();
   for (int g = 0; g < G; ++g) {
@@ -475,6 +495,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
                                     : MmaOp<T>::from_float(val);
     }
   }
+  MSGL_TRD(9, clock64());      // merged rows written
+  MSGL_TRD(10, trace_wall());
 }
 
 }  // namespace msgl

@@ -53,30 +53,6 @@
 
 namespace msgl {
 
-// Development aid, compiled in only with -DMSGL_TRACE: one record per CTA (SM, wall-clock entry
-// and exit, cycle counts at the milestones of softmax group 0) read back through
-// msgl_debug_read_cta_trace.
-#ifdef MSGL_TRACE
-constexpr int kTraceCtas = 8192;
-__device__ long long g_cta_trace[kTraceCtas][32];
-__device__ __forceinline__ long long trace_wall() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ int trace_smid() {
-  int s;
-  asm volatile("mov.u32 %0, %%smid;" : "=r"(s));
-  return s;
-}
-#define MSGL_TR(slot, value)                                                   \
-  do {                                                                         \
-    if (blockIdx.x < kTraceCtas) g_cta_trace[blockIdx.x][slot] = (value);      \
-  } while (0)
-#else
-#define MSGL_TR(slot, value) do { } while (0)
-#endif
-
 constexpr int kTcSub = 128;       // rows per sub-tile (= MMA M)
 
 // Shape of a CTA.  NSUB = 2: 256 query rows, 16 warps, all 512 TMEM columns, 160 KB K/V
@@ -316,8 +292,12 @@ template <typename T, int HD, int NSUB, int NSW, typename Shape>
 __device__ __noinline__ void merge_kv_splits(const MergeArgs p, TcBarriers& bars,
                                              unsigned char* smem_raw, uint32_t smem0,
                                              volatile int* abort_flag, int nsp, int64_t slot0,
+                                             int64_t slot_base, int64_t slot_stride,
                                              int rows_valid, int pk0, int q_begin, int h) {
+  // partial sp of the unit sits in scratch slot slot0 (sp = 0) or slot_base + sp * slot_stride;
+  // the barriers it uses (msync, mload) must be in their initial phase
   constexpr int BM = Shape::kBM;
+  auto slot_of = [&](int sp) { return sp == 0 ? slot0 : slot_base + sp * slot_stride; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.group;
   __threadfence();
@@ -356,10 +336,10 @@ __device__ __noinline__ void merge_kv_splits(const MergeArgs p, TcBarriers& bars
   for (int half = 0; half * 64 < rows_valid && ok; ++half) {
     const int hv = min(64, rows_valid - half * 64);
     auto src_o = [&](int sp) {
-      return p.part_o + ((slot0 + static_cast<int64_t>(sp) * p.hkv) * BM + half * 64) * HD;
+      return p.part_o + (slot_of(sp) * BM + half * 64) * HD;
     };
     auto src_ml = [&](int sp) {
-      return p.part_ml + ((slot0 + static_cast<int64_t>(sp) * p.hkv) * BM + half * 64) * 2;
+      return p.part_ml + (slot_of(sp) * BM + half * 64) * 2;
     };
     auto issue_load = [&](int sp, int b3) {   // b3: 0 = A, 1 + b = incoming buffer b
       const uint32_t bar = smem_u32(&bars.mload[b3]);
@@ -1227,7 +1207,7 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD, PAGED>::kThreads,
       // the softmax warps merge (a function of its own: its registers do not weigh on the main loop)
       const MergeArgs ma{p.part_o, p.part_ml, p.out, p.gate, p.status, p.hq, p.hkv, p.group};
       merge_kv_splits<T, HD, NSUB, kMmaWarp, Shape>(ma, bars, smem_raw, smem0, abort_flag, nsp, slot0,
-                                                    rows_valid, pk0, sq.q_begin, h);
+                                                    slot0, p.hkv, rows_valid, pk0, sq.q_begin, h);
 #ifdef MSGL_TRACE
       if (tid == 0) MSGL_TR(14, clock64());
 #endif
