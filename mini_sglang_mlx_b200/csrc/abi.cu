@@ -195,6 +195,7 @@ struct PrefillPlan {
   int kv_chunk;        // 0 = no kv split
   int64_t items;       // grid.x
   size_t part_o_bytes, part_ml_bytes, plan_bytes;
+  bool fused_merge;    // the CTA that arrives last at a unit merges it (else: a second launch)
 };
 
 
@@ -243,6 +244,13 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
     if (chunk < 1024) chunk = 1024;
     chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
+    // One CTA merges a unit at the pace of one SM's L2 port (about 17 GB/s measured with the
+    // rows of the other splits in flight): fine for the draft-block and verify units (tens of
+    // KB, a few us, and no second launch), not for a 256-row unit of many pieces (128 query
+    // tokens over 32768 keys: 9 x 256 rows x 512 B = 1.2 MB, 70 us against 4 us spread over the
+    // grid of a second launch).
+    const int64_t rows = std::min<int64_t>(BM, static_cast<int64_t>(max_len_extend) * G);
+    pl.fused_merge = pieces * rows * head_dim * 4 <= 256 * 1024;
   }
 #ifdef MSGL_TRACE
   // development builds only: a key-range piece length to try instead of the policy's
@@ -766,7 +774,8 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   p.status = reinterpret_cast<int*>(ws);
   if (pl.kv_chunk > 0) {
-    p.tickets = reinterpret_cast<int*>(ws + 256);   // at most kPrefillTickets units when split
+    // at most kPrefillTickets units when split; no counters = the merge is a launch of its own
+    p.tickets = pl.fused_merge ? reinterpret_cast<int*>(ws + 256) : nullptr;
     p.part_ml = reinterpret_cast<float*>(ws + kStatusBytes + pl.plan_bytes);
     p.part_o = reinterpret_cast<float*>(ws + kStatusBytes + pl.plan_bytes + pl.part_ml_bytes);
   }
@@ -785,10 +794,12 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
   dim3 grid(static_cast<unsigned>(pl.items * num_kv_heads));
   const bool short_q = prefill_short_q(max_len_extend, p.group, head_dim);
   cudaError_t e;
-  auto launch = [&](auto kernel, int threads, int smem) -> cudaError_t {
+  auto launch = [&](auto kernel, auto merge, int threads, int smem) -> cudaError_t {
     cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
     kernel<<<grid, threads, smem, s>>>(p, tm_k, tm_v, tm_q);
+    if (pl.kv_chunk > 0 && !pl.fused_merge)
+      return launch_dependent(merge, dim3(grid.x, msgl::kMergeSlices), dim3(msgl::kMergeWarps * 32), s, p);
     return cudaSuccess;
   };
   // per element type: head_dim 256 / short query blocks / long chunks, each per-token or paged
@@ -800,14 +811,17 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
     using P1 = msgl::TcShape<1, 128, true>;
     using P2 = msgl::TcShape<2, 128, true>;
     using P1w = msgl::TcShape<1, 256, true>;
+    auto m1w = msgl::prefill_merge_kernel<T, 256, S1w::kBM>;
+    auto m1 = msgl::prefill_merge_kernel<T, 128, S1::kBM>;
+    auto m2 = msgl::prefill_merge_kernel<T, 128, S2::kBM>;
     if (head_dim == 256)
-      return pages ? launch(msgl::prefill_tc_kernel<T, 64, 1, 256, true>, P1w::kThreads, P1w::kSmemBytes)
-                   : launch(msgl::prefill_tc_kernel<T, 64, 1, 256>, S1w::kThreads, S1w::kSmemBytes);
+      return pages ? launch(msgl::prefill_tc_kernel<T, 64, 1, 256, true>, m1w, P1w::kThreads, P1w::kSmemBytes)
+                   : launch(msgl::prefill_tc_kernel<T, 64, 1, 256>, m1w, S1w::kThreads, S1w::kSmemBytes);
     if (short_q)
-      return pages ? launch(msgl::prefill_tc_kernel<T, 64, 1, 128, true>, P1::kThreads, P1::kSmemBytes)
-                   : launch(msgl::prefill_tc_kernel<T, 64, 1>, S1::kThreads, S1::kSmemBytes);
-    return pages ? launch(msgl::prefill_tc_kernel<T, 128, 2, 128, true>, P2::kThreads, P2::kSmemBytes)
-                 : launch(msgl::prefill_tc_kernel<T, 128, 2>, S2::kThreads, S2::kSmemBytes);
+      return pages ? launch(msgl::prefill_tc_kernel<T, 64, 1, 128, true>, m1, P1::kThreads, P1::kSmemBytes)
+                   : launch(msgl::prefill_tc_kernel<T, 64, 1>, m1, S1::kThreads, S1::kSmemBytes);
+    return pages ? launch(msgl::prefill_tc_kernel<T, 128, 2, 128, true>, m2, P2::kThreads, P2::kSmemBytes)
+                 : launch(msgl::prefill_tc_kernel<T, 128, 2>, m2, S2::kThreads, S2::kSmemBytes);
   };
   e = dtype == MSGL_DTYPE_BF16 ? dispatch(__nv_bfloat16{}) : dispatch(__half{});
   if (e != cudaSuccess) return cuda_fail("paged_prefill_attention", e);

@@ -266,18 +266,19 @@ struct TcBarriers {
   // j-2 from j by parity alone)
   uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];
   // kv splits: stage[i] synchronises the 128 threads of softmax group i around the staging
-  // buffer of its partial; while the last arriver merges, msync synchronises all softmax
-  // threads and mload[b] counts the bytes of the bulk load into merge buffer b
-  uint64_t stage[2], msync, mload[6];
+  // buffer of its partial
+  uint64_t stage[2];
 };
 
-// Merge of the kv-split partials of one (sequence, q tile, head) unit by the CTA that arrived
-// last, run by its NSW softmax warps, 64 rows at a time.  Every role of the CTA is done, so the
-// whole dynamic shared memory is free: buffer A takes split 0 and becomes the accumulator,
-// buffers B0 / B1 take the further splits in turn, each as one bulk load of a 64-row blob
-// (issued two splits ahead); their (m, l) pairs come by ordinary loads.  A warp owns RU rows at a
-// time and a lane 4 or 8 columns of a row; the last split is folded in and the rows are written
-// out in one go.
+// Merge of rows [row_lo, row_hi) of the kv-split partials of one (sequence, q tile, head) unit,
+// run by NSW warps: all rows by the CTA that arrived last at the unit's counter, or (large
+// units: one SM would pull megabytes through its own L2 port) a slice of the rows by each CTA
+// of a second, dependent launch.  A warp owns RU rows at a time and a lane 4 or 8 columns
+// of a row; per row it takes the largest split maximum M (lane-strided loads of the (m, l)
+// pairs, one warp reduction), then walks the splits once: out = sum_s 2^(m_s - M) O_s /
+// sum_s 2^(m_s - M) l_s, the rows of O_s read straight from scratch (they sit in L2: the
+// splits have just written them), all splits of the RU rows in flight together.  No shared
+// memory, no synchronisation between warps.
 // (The few fields of the launch parameters it needs come by value: taking the address of the
 // kernel's parameter block would make the kernel keep a local copy of it.)
 struct MergeArgs {
@@ -285,174 +286,108 @@ struct MergeArgs {
   const float* part_ml;
   void* out;
   const void* gate;
-  int* status;
-  int hq, hkv, group;
+  int hq, group;
 };
-template <typename T, int HD, int NSUB, int NSW, typename Shape>
-__device__ __noinline__ void merge_kv_splits(const MergeArgs p, TcBarriers& bars,
-                                             unsigned char* smem_raw, uint32_t smem0,
-                                             volatile int* abort_flag, int nsp, int64_t slot0,
-                                             int64_t slot_base, int64_t slot_stride,
-                                             int rows_valid, int pk0, int q_begin, int h) {
-  // partial sp of the unit sits in scratch slot slot0 (sp = 0) or slot_base + sp * slot_stride;
-  // the barriers it uses (msync, mload) must be in their initial phase
-  constexpr int BM = Shape::kBM;
-  auto slot_of = [&](int sp) { return sp == 0 ? slot0 : slot_base + sp * slot_stride; };
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+template <typename T, int HD, int NSW, int BM, int RU, int SU>
+__device__ __noinline__ void merge_kv_splits(const MergeArgs p, int nsp, int64_t slot0,
+                                             int64_t slot_stride, int row_lo, int row_hi, int pk0,
+                                             int q_begin, int h) {
+  // partial sp of the unit sits in scratch slot slot0 + sp * slot_stride; in scratch the
+  // 16-byte chunk c of row r sits at chunk position c ^ (r & 31) of the row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.group;
   __threadfence();
-  fence_proxy_async_all();
-  constexpr int RBF = HD * 4;
-  constexpr uint32_t kBlob = 64 * RBF;
   constexpr int VPL = HD / 32;          // output columns per lane
-    constexpr int RU = 4;                 // rows a warp works on at a time (independent chains)
-  // (m, l) of the accumulator and of the two incoming splits: behind the three blobs where
-  // the shape has the room, else in static shared memory
-  // NB incoming buffers: as many as the shape's shared memory holds beside A, at most 5
-  constexpr int kRoom = NSUB * Shape::kQTileBytes + Shape::kRingBytes;
-  constexpr int NB = (kRoom - 4096) / static_cast<int>(kBlob) - 1 >= 5 ? 5 : 2;
-  constexpr bool kMlDynamic = (1 + NB) * kBlob + 4096 <= kRoom;
-  static_assert((1 + NB) * kBlob <= kRoom, "merge buffers");
-  __shared__ __align__(16) float s_ml_static[kMlDynamic ? 4 : 128 + 128 * NB];
-  const uint32_t buf_a = smem0;
-  unsigned char* gen_a = smem_raw + (smem0 - smem_u32(smem_raw));
-  float* ml_base = kMlDynamic ? reinterpret_cast<float*>(gen_a + (1 + NB) * kBlob) : s_ml_static;
-  float* s_m = ml_base;                                  // [64]
-  float* s_l = ml_base + 64;                             // [64]
-  float2* s_mlin = reinterpret_cast<float2*>(ml_base + 128);   // [NB][64]
-  const uint32_t bar_ms = smem_u32(&bars.msync);
-  uint32_t ms_phase = 0, ld_phase[1 + NB];
-#pragma unroll
-  for (int b3 = 0; b3 <= NB; ++b3) ld_phase[b3] = 0;
-  bool ok = true;
-  auto group_sync = [&]() {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_ms);
-    ok = mbar_wait_warp(bar_ms, ms_phase, abort_flag);
-    ms_phase ^= 1;
-  };
+  constexpr int NV = VPL / 4;           // 16-byte pieces per lane
+  // RU rows a warp works on at a time, SU splits whose loads are issued together
   T* out = static_cast<T*>(p.out);
   const T* gate = static_cast<const T*>(p.gate);
-  for (int half = 0; half * 64 < rows_valid && ok; ++half) {
-    const int hv = min(64, rows_valid - half * 64);
-    auto src_o = [&](int sp) {
-      return p.part_o + (slot_of(sp) * BM + half * 64) * HD;
-    };
-    auto src_ml = [&](int sp) {
-      return p.part_ml + (slot_of(sp) * BM + half * 64) * 2;
-    };
-    auto issue_load = [&](int sp, int b3) {   // b3: 0 = A, 1 + b = incoming buffer b
-      const uint32_t bar = smem_u32(&bars.mload[b3]);
-      mbar_arrive_expect_tx(bar, kBlob);
-      bulk_load(buf_a + b3 * kBlob, src_o(sp), kBlob, bar);
-    };
-    if (tid == 0) {
-      issue_load(0, 0);
-      for (int sp = 1; sp < nsp && sp <= NB; ++sp) issue_load(sp, sp);
-    }
-    if (tid < hv) {
-      float2 mls[1 + NB];
+  for (int r0 = row_lo + warp * RU; r0 < row_hi; r0 += NSW * RU) {
+    int rr[RU];
 #pragma unroll
-      for (int sp = 0; sp <= NB; ++sp)
-        mls[sp] = sp < nsp ? __ldcg(reinterpret_cast<const float2*>(src_ml(sp)) + tid) : make_float2(0.f, 0.f);
-      s_m[tid] = mls[0].x;
-      s_l[tid] = mls[0].y;
+    for (int k = 0; k < RU; ++k) rr[k] = min(r0 + k, row_hi - 1);
+    float2 ml[SU][RU];
+    float4 x[SU][RU][NV];
+    auto load_splits = [&](int s0) {   // splits s0 .. s0+SU-1 of the RU rows (clamped: re-reads the last)
 #pragma unroll
-      for (int sp = 1; sp <= NB; ++sp) s_mlin[(sp - 1) * 64 + tid] = mls[sp];
-    }
-    ok = mbar_wait_warp(smem_u32(&bars.mload[0]), ld_phase[0], abort_flag);
-    ld_phase[0] ^= 1;
-    if (!ok) break;
-    for (int sp = 1; sp < nsp; ++sp) {
-      const int b = (sp - 1) % NB;
-      const bool final_split = sp == nsp - 1;   // fold it in and write the rows out in one go
-      ok = mbar_wait_warp(smem_u32(&bars.mload[1 + b]), ld_phase[1 + b], abort_flag);
-      ld_phase[1 + b] ^= 1;
-      if (!ok) break;
-      group_sync();                       // the (m, l) pairs of this split are in place
-      if (!ok) break;
-      const unsigned char* gen_b = gen_a + (1 + b) * kBlob;
-      for (int r0 = warp * RU; r0 < hv; r0 += NSW * RU) {
-        float a[RU], wgt[RU], mn[RU], ln[RU];
+      for (int u = 0; u < SU; ++u) {
+        const int sp = min(s0 + u, nsp - 1);
+        const int64_t row0 = (slot0 + sp * slot_stride) * BM;
 #pragma unroll
         for (int k = 0; k < RU; ++k) {
-          const int rr = min(r0 + k, hv - 1);
-          const float2 mls = s_mlin[b * 64 + rr];
-          const float mo = s_m[rr], lo = s_l[rr];
-          mn[k] = fmaxf(mo, mls.x);
-          a[k] = mo == -INFINITY ? 0.f : fast_exp2(mo - mn[k]);
-          wgt[k] = mls.x == -INFINITY ? 0.f : fast_exp2(mls.x - mn[k]);
-          ln[k] = lo * a[k] + wgt[k] * mls.y;
-        }
-        __syncwarp();                     // every lane has read (m, l) before lane 0 updates them
-        float4 acc[RU][VPL / 4];
+          ml[u][k] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (row0 + rr[k]) * 2));
 #pragma unroll
-        for (int k = 0; k < RU; ++k) {
-          const int rr = min(r0 + k, hv - 1);
-#pragma unroll
-          for (int e4 = 0; e4 < VPL / 4; ++e4) {
-            const int pos = ((lane * (VPL / 4) + e4) ^ (rr & 31)) << 4;
-            const float4 x = *reinterpret_cast<const float4*>(gen_b + rr * RBF + pos);
-            float4 y = *reinterpret_cast<const float4*>(gen_a + rr * RBF + pos);
-            y.x = y.x * a[k] + wgt[k] * x.x;
-            y.y = y.y * a[k] + wgt[k] * x.y;
-            y.z = y.z * a[k] + wgt[k] * x.z;
-            y.w = y.w * a[k] + wgt[k] * x.w;
-            acc[k][e4] = y;
-          }
-        }
-#pragma unroll
-        for (int k = 0; k < RU; ++k) {
-          const int rr = r0 + k;
-          if (rr >= hv) break;
-          if (!final_split) {
-#pragma unroll
-            for (int e4 = 0; e4 < VPL / 4; ++e4) {
-              const int pos = ((lane * (VPL / 4) + e4) ^ (rr & 31)) << 4;
-              *reinterpret_cast<float4*>(gen_a + rr * RBF + pos) = acc[k][e4];
-            }
-            if (lane == 0) {
-              s_m[rr] = mn[k];
-              s_l[rr] = ln[k];
-            }
-          } else {
-            const float invd = ln[k] > 0.f ? 1.f / ln[k] : 0.f;
-            const int pkr = pk0 + half * 64 + rr;
-            const int tlr = pkr / G, gr = pkr - tlr * G;
-            const int64_t oi =
-                (static_cast<int64_t>(q_begin + tlr) * p.hq + static_cast<int64_t>(h) * G + gr) * HD +
-                lane * VPL;
-            alignas(16) T vals[VPL];
-#pragma unroll
-            for (int e4 = 0; e4 < VPL / 4; ++e4) {
-              const float f[4] = {acc[k][e4].x * invd, acc[k][e4].y * invd, acc[k][e4].z * invd,
-                                  acc[k][e4].w * invd};
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                vals[4 * e4 + e] =
-                    gate ? apply_gate<T>(f[e], gate[oi + 4 * e4 + e]) : MmaOp<T>::from_float(f[e]);
-            }
-            if constexpr (VPL == 4)
-              *reinterpret_cast<uint2*>(out + oi) = *reinterpret_cast<const uint2*>(vals);
-            else
-              *reinterpret_cast<uint4*>(out + oi) = *reinterpret_cast<const uint4*>(vals);
+          for (int e4 = 0; e4 < NV; ++e4) {
+            const int pos = ((lane * NV + e4) ^ (rr[k] & 31)) << 2;   // in floats
+            x[u][k][e4] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (row0 + rr[k]) * HD + pos));
           }
         }
       }
-      group_sync();                       // everyone is done with buffer b and its (m, l)
-      if (!ok) break;
-      if (sp + NB < nsp) {
-        if (tid == 0) {
-          fence_proxy_async_all();
-          issue_load(sp + NB, 1 + b);
+    };
+    load_splits(0);   // in flight while the row maxima are found
+    float M[RU], L[RU];
+#pragma unroll
+    for (int k = 0; k < RU; ++k) {
+      float m = -INFINITY;
+      for (int sp = lane; sp < nsp; sp += 32)
+        m = fmaxf(m, __ldcg(p.part_ml + ((slot0 + sp * slot_stride) * BM + rr[k]) * 2));
+      M[k] = m;
+      L[k] = 0.f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int k = 0; k < RU; ++k) M[k] = fmaxf(M[k], __shfl_xor_sync(0xffffffffu, M[k], o));
+    }
+    float4 acc[RU][NV];
+#pragma unroll
+    for (int k = 0; k < RU; ++k)
+#pragma unroll
+      for (int e4 = 0; e4 < NV; ++e4) acc[k][e4] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < nsp; s0 += SU) {
+      if (s0 > 0) load_splits(s0);
+#pragma unroll
+      for (int u = 0; u < SU; ++u) {
+        if (s0 + u >= nsp) break;
+#pragma unroll
+        for (int k = 0; k < RU; ++k) {
+          const float w = ml[u][k].x == -INFINITY ? 0.f : fast_exp2(ml[u][k].x - M[k]);
+          L[k] += w * ml[u][k].y;
+#pragma unroll
+          for (int e4 = 0; e4 < NV; ++e4) {
+            acc[k][e4].x += w * x[u][k][e4].x;
+            acc[k][e4].y += w * x[u][k][e4].y;
+            acc[k][e4].z += w * x[u][k][e4].z;
+            acc[k][e4].w += w * x[u][k][e4].w;
+          }
         }
-        if (tid < hv)
-          s_mlin[b * 64 + tid] = __ldcg(reinterpret_cast<const float2*>(src_ml(sp + NB)) + tid);
       }
     }
-    if (!ok) break;
+#pragma unroll
+    for (int k = 0; k < RU; ++k) {
+      if (r0 + k >= row_hi) break;
+      const float invd = L[k] > 0.f ? 1.f / L[k] : 0.f;
+      const int pkr = pk0 + r0 + k;
+      const int tlr = pkr / G, gr = pkr - tlr * G;
+      const int64_t oi =
+          (static_cast<int64_t>(q_begin + tlr) * p.hq + static_cast<int64_t>(h) * G + gr) * HD +
+          lane * VPL;
+      alignas(16) T vals[VPL];
+#pragma unroll
+      for (int e4 = 0; e4 < NV; ++e4) {
+        const float f[4] = {acc[k][e4].x * invd, acc[k][e4].y * invd, acc[k][e4].z * invd,
+                            acc[k][e4].w * invd};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          vals[4 * e4 + e] =
+              gate ? apply_gate<T>(f[e], gate[oi + 4 * e4 + e]) : MmaOp<T>::from_float(f[e]);
+      }
+      if constexpr (VPL == 4)
+        *reinterpret_cast<uint2*>(out + oi) = *reinterpret_cast<const uint2*>(vals);
+      else
+        *reinterpret_cast<uint4*>(out + oi) = *reinterpret_cast<const uint4*>(vals);
+    }
   }
-  if (!ok && p.status && tid == 0) atomicExch(p.status, 1);
 }
 
 template <typename T, int BN, int NSUB, int HD = 128, bool PAGED = false>
@@ -515,8 +450,6 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD, PAGED>::kThreads,
       mbar_init(bar_full(bf), PAGED ? 33 : NPROD);
       mbar_init(bar_empty(bf), 1);
     }
-    mbar_init(smem_u32(&bars.msync), kMmaWarp);          // one arrival per softmax warp
-    for (int b3 = 0; b3 < 6; ++b3) mbar_init(smem_u32(&bars.mload[b3]), 1);
     for (int i = 0; i < NSUB; ++i) {
       mbar_init(smem_u32(&bars.stage[i]), SUB / 32);     // one arrival per warp of the group
       mbar_init(bar_sf(i, 0), 1);
@@ -1184,7 +1117,7 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD, PAGED>::kThreads,
   // ---- kv splits: the CTA that arrives last at the unit's counter merges the partials
   // (out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s) and writes the output rows; no second
   // launch.  The counter goes back to zero for the next call.
-  if (p.kv_chunk > 0 && sq.nsplit > 1) {
+  if (p.kv_chunk > 0 && sq.nsplit > 1 && p.tickets != nullptr) {
     __shared__ int s_last;
     const int nsp = sq.nsplit;
     const int64_t slot0 = static_cast<int64_t>(it.base + qt * nsp) * p.hkv + h;  // split s: slot0 + s * hkv
@@ -1203,16 +1136,47 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD, PAGED>::kThreads,
       MSGL_TR(13, s_last);
     }
 #endif
-    if (s_last != 0 && warp < kMmaWarp) {
+    // (where the register pool was re-balanced only the softmax warps have the registers)
+    constexpr int kMergers = Shape::kRebalanceRegs ? kMmaWarp : Shape::kWarps;
+    if (s_last != 0 && warp < kMergers) {
       // the softmax warps merge (a function of its own: its registers do not weigh on the main loop)
-      const MergeArgs ma{p.part_o, p.part_ml, p.out, p.gate, p.status, p.hq, p.hkv, p.group};
-      merge_kv_splits<T, HD, NSUB, kMmaWarp, Shape>(ma, bars, smem_raw, smem0, abort_flag, nsp, slot0,
-                                                    slot0, p.hkv, rows_valid, pk0, sq.q_begin, h);
+      const MergeArgs ma{p.part_o, p.part_ml, p.out, p.gate, p.hq, p.group};
+      // (2 rows x 2 splits in flight per lane: what the register cap of the main kernel holds)
+      merge_kv_splits<T, HD, kMergers, BM, 2, 2>(ma, nsp, slot0, p.hkv, 0, rows_valid,
+                                                                    pk0, sq.q_begin, h);
 #ifdef MSGL_TRACE
       if (tid == 0) MSGL_TR(14, clock64());
 #endif
     }
   }
+}
+
+// Second launch of a split call whose units are too large for one CTA to merge: same grid as the
+// attention kernel; the CTA that maps to split s of a unit merges the s-th slice of the unit's
+// rows (gridDim.y CTAs share a slice), so the work is spread over as many SMs as the attention
+// itself was, a row or two per warp.
+constexpr int kMergeWarps = 8;
+constexpr int kMergeSlices = 4;
+template <typename T, int HD, int BM>
+__global__ void __launch_bounds__(kMergeWarps * 32) prefill_merge_kernel(const PrefillParams p) {
+  __shared__ int s_scratch[4 * kSortedBatchMax];
+  grid_dependency_wait();   // the partials come from the attention kernel
+  ItemCoord it;
+  if (!find_item<kMergeWarps * 32>(p, static_cast<int>(blockIdx.x), BM, s_scratch, it)) return;
+  const SeqShape sq = load_seq_shape(p, it.b, BM);
+  const int nsp = sq.nsplit;
+  if (nsp <= 1) return;     // an unsplit unit's rows were written by the attention kernel
+  const int pk0 = it.qt * BM;
+  const int rows_valid = min(BM, sq.tq * p.group - pk0);
+  const int parts = nsp * static_cast<int>(gridDim.y);
+  const int per = (rows_valid + parts - 1) / parts;
+  const int row_lo = (it.split * static_cast<int>(gridDim.y) + static_cast<int>(blockIdx.y)) * per;
+  const int row_hi = min(rows_valid, row_lo + per);
+  if (row_lo >= row_hi) return;
+  const int64_t slot0 = static_cast<int64_t>(it.base + it.qt * nsp) * p.hkv + it.h;
+  const MergeArgs ma{p.part_o, p.part_ml, p.out, p.gate, p.hq, p.group};
+  merge_kv_splits<T, HD, kMergeWarps, BM, 2, 4>(ma, nsp, slot0, p.hkv, row_lo, row_hi, pk0, sq.q_begin,
+                                                 it.h);
 }
 
 }  // namespace msgl
