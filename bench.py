@@ -173,6 +173,17 @@ def _make_workload(name: str, device, rank: int):
     if name.startswith("cfg5b"):
         _, c, p = name.split("_")
         return S.cfg5b_prefill_point(int(c), int(p), seed=606 + seed_shift, device=device)
+    if name.startswith("d256p_"):   # head_dim 256 prefill: d256p_<kv heads>_<q heads>_<q len>[_<prefix>]
+        f = [int(x) for x in name.split("_")[1:]]
+        return S.d256_prefill_point(f[0], f[1], f[2], f[3] if len(f) > 3 else 0, device=device)
+    if name.startswith("d256d_"):   # head_dim 256 decode: d256d_<kv heads>_<q heads>_<kv len>[_<batch>]
+        from mini_sglang_mlx_b200.attention import compute_num_kv_splits
+        f = [int(x) for x in name.split("_")[1:]]
+        w = S.d256_decode_point(f[0], f[1], f[2], f[3] if len(f) > 3 else 1, device=device)
+        splits = compute_num_kv_splits(w.kv_lens, w.hkv)
+        w.num_kv_splits = torch.tensor(splits, dtype=torch.int32, device=device)
+        w.max_kv_splits = max(splits)
+        return w
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -197,9 +208,15 @@ def run_op(w):
 
 
 def launches_per_step(w) -> int:
-    """Kernels of this library per operator call: one.  The key-range splits of the decode kernel
-    and of the prefill kernel are merged by the CTA that finishes last, inside the same launch."""
-    return 1
+    """Kernels of this library per operator call.  Decode: one (its key-range splits are merged
+    by the CTA that finishes last).  Prefill: one, or two when the splits of a large (sequence,
+    query tile, head) unit are merged by a second, dependent launch; the library says which."""
+    if w.kind == "decode":
+        return 1
+    from mini_sglang_mlx_b200 import _lib
+    return int(_lib.lib().msgl_prefill_launch_count(
+        w.batch, int(w.q.shape[0]), int(sum(w.kv_lens)), w.hq, w.hkv, w.head_dim,
+        int(w.max_len_extend), int(w.sliding_window_size), 1 if w.index == "page" else 0))
 
 
 def barrier(dist_on: bool):

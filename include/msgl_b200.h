@@ -34,6 +34,9 @@
  *   prefix_lens            (batch) int32, absolute position of a sequence's first query row
  *   num_kv_splits          (batch) int32, split-KV hint per sequence
  * Grouped-query mapping: kv_head = q_head / (num_q_heads / num_kv_heads).
+ * q, out, gate, the pools and every workspace must be 16-byte aligned (the
+ * kernels move them in 16-byte pieces); the attention ops return MSGL_BAD_ARG
+ * otherwise.
  */
 #ifndef MSGL_B200_H_
 #define MSGL_B200_H_
@@ -175,6 +178,17 @@ int msgl_paged_decode_attention_gated(
 size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, int num_q_heads,
                                     int num_kv_heads, int head_dim, int max_len_extend,
                                     int sliding_window_size);
+
+/*
+ * Kernel launches one prefill call of this shape makes: 1, or 2 when the key
+ * range is split and a (sequence, query tile, head) unit is too large for the
+ * CTA that finishes last to merge (the merge is then a second launch, chained
+ * to the first with programmatic stream serialization).  page_granular != 0
+ * asks for the *_p16 entry points.  No counterpart in the reference.
+ */
+int msgl_prefill_launch_count(int batch, int total_q, int64_t total_kv, int num_q_heads,
+                              int num_kv_heads, int head_dim, int max_len_extend,
+                              int sliding_window_size, int page_granular);
 
 /*
  * Paged prefill / extend attention over prefix + new tokens with the four

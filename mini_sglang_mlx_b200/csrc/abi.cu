@@ -502,8 +502,8 @@ int launch_decode(const msgl::DecodeParams& p, int head_dim, cudaStream_t s, con
     return paged ? launch(msgl::decode_partial_kernel<T, 128, kDecWarps, kDecStages, true>, smem + 1024)
                  : launch(msgl::decode_partial_kernel<T, 128, kDecWarps, kDecStages>, smem);
   }
-  // head_dim 256: 512-byte token rows, two ring stages per warp (128 KB per CTA)
-  constexpr int kStages256 = 2;
+  // head_dim 256: 512-byte token rows, 16 KB per stage
+  constexpr int kStages256 = 3;   // 192 KB of the 227 KB: one CTA per SM, three 16-token groups in flight per warp
   constexpr int smem = kDecWarps * kStages256 * 2 * msgl::kDecodeGroupTokens * 512;
   return paged ? launch(msgl::decode_partial_kernel<T, 256, kDecWarps, kStages256, true>, smem + 1024)
                : launch(msgl::decode_partial_kernel<T, 256, kDecWarps, kStages256>, smem);
@@ -523,6 +523,8 @@ struct PageIndex {
 // header when there are at most kTicketSlots of them; a larger batch gets a region of its own
 // behind the header, cleared by every call (the workspace query is not told the KV head
 // count, so it sizes that region for the query heads).
+static bool aligned16(const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; }
+
 static size_t decode_ticket_bytes(int batch, int num_q_heads) {
   const size_t n = static_cast<size_t>(batch) * num_q_heads;
   return n <= kTicketSlots ? 0 : (n * sizeof(int) + 255) / 256 * 256;
@@ -567,6 +569,10 @@ static int decode_impl(const void* q, const void* k_cache, const void* v_cache,
     return fail(MSGL_BAD_SHAPE, std::string(op) + "batch and num_kv_heads must be <= 65535");
   if (!q || !k_cache || !v_cache || !out || (!pages && (!kv_indptr || !kv_indices)))
     return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out) ||
+      !aligned16(gate) || !aligned16(workspace))
+    return fail(MSGL_BAD_ARG, std::string(op) + "q, the pools, out, gate and the workspace must be "
+                                                "16-byte aligned");
   CUtensorMap tm_k, tm_v;
   std::memset(&tm_k, 0, sizeof(tm_k));
   std::memset(&tm_v, 0, sizeof(tm_v));
@@ -706,6 +712,20 @@ size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, in
   return kStatusBytes + pl.plan_bytes + pl.part_ml_bytes + pl.part_o_bytes;
 }
 
+int msgl_prefill_launch_count(int batch, int total_q, int64_t total_kv, int num_q_heads,
+                              int num_kv_heads, int head_dim, int max_len_extend,
+                              int sliding_window_size, int page_granular) {
+  if (batch <= 0 || total_q <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 ||
+      num_q_heads % num_kv_heads != 0)
+    return 1;
+  const int sms = sm_count_cached();
+  (void)page_granular;   // both index granularities split alike
+  const PrefillPlan pl = plan_prefill(batch, total_q, total_kv, num_q_heads, num_kv_heads,
+                                      head_dim, max_len_extend, sliding_window_size,
+                                      sms > 0 ? sms : 148);
+  return (pl.kv_chunk > 0 && !pl.fused_merge) ? 2 : 1;
+}
+
 static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
                         const int32_t* qo_indptr, const int32_t* kv_indptr,
                         const int32_t* kv_indices, const int32_t* prefix_lens, const void* gate,
@@ -734,6 +754,10 @@ static int prefill_impl(const void* q, const void* k_cache, const void* v_cache,
   if (!q || !k_cache || !v_cache || !qo_indptr || !prefix_lens || !out ||
       (!pages && (!kv_indptr || !kv_indices)))
     return fail(MSGL_BAD_ARG, std::string(op) + "null tensor pointer");
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out) ||
+      !aligned16(gate) || !aligned16(workspace))
+    return fail(MSGL_BAD_ARG, std::string(op) + "q, the pools, out, gate and the workspace must be "
+                                                "16-byte aligned");
   const int sms = sm_count_cached();
   if (sms <= 0) return fail(MSGL_CUDA_ERROR, std::string(op) + "cannot query the device");
   CUtensorMap tm_k, tm_v;

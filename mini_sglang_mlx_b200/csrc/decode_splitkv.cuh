@@ -475,25 +475,60 @@ __global__ void __launch_bounds__(NWARPS * 32)
   MSGL_TRD(11, s_last);
   if (s_last == 0) return;
   __threadfence();
-  for (int g = 0; g < G; ++g) {
+  // a warp per query head, a lane per 4 (8) output columns; the splits' rows come straight from
+  // scratch (L2), four splits in flight per lane
+  constexpr int VPL = HD / 32, NV = VPL / 4;
+  for (int g = warp; g < G; g += NWARPS) {
     const int64_t hq_idx = static_cast<int64_t>(b) * p.hq + static_cast<int64_t>(h) * G + g;
     const float* lse = p.part_lse + hq_idx * p.max_splits;
-    const float* po = p.part_o + hq_idx * p.max_splits * HD;
+    const float* po = p.part_o + hq_idx * p.max_splits * HD + lane * VPL;
     float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(lse + s));
-    for (int d = threadIdx.x; d < HD; d += NWARPS * 32) {
-      float num = 0.f, den = 0.f;
-      if (M != -INFINITY) {
-        for (int s = 0; s < splits; ++s) {
-          const float w = __expf(__ldcg(lse + s) - M);
+    for (int s = lane; s < splits; s += 32) M = fmaxf(M, __ldcg(lse + s));
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+    float num[VPL];
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) num[e] = 0.f;
+    float den = 0.f;
+    if (M != -INFINITY) {
+      for (int s0 = 0; s0 < splits; s0 += 4) {
+        float ls[4];
+        float4 x[4][NV];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int sp = min(s0 + u, splits - 1);
+          ls[u] = __ldcg(lse + sp);
+#pragma unroll
+          for (int e4 = 0; e4 < NV; ++e4)
+            x[u][e4] = __ldcg(reinterpret_cast<const float4*>(po + static_cast<int64_t>(sp) * HD) + e4);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (s0 + u >= splits) break;
+          const float w = __expf(ls[u] - M);
           den += w;
-          num += w * __ldcg(po + s * HD + d);
+#pragma unroll
+          for (int e4 = 0; e4 < NV; ++e4) {
+            num[4 * e4 + 0] += w * x[u][e4].x;
+            num[4 * e4 + 1] += w * x[u][e4].y;
+            num[4 * e4 + 2] += w * x[u][e4].z;
+            num[4 * e4 + 3] += w * x[u][e4].w;
+          }
         }
       }
-      const float val = den > 0.f ? num / den : 0.f;
-      out[hq_idx * HD + d] = p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[hq_idx * HD + d])
-                                    : MmaOp<T>::from_float(val);
     }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    const int64_t oi = hq_idx * HD + lane * VPL;
+    alignas(16) T vals[VPL];
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) {
+      const float val = num[e] * inv;
+      vals[e] = p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[oi + e]) : MmaOp<T>::from_float(val);
+    }
+    if constexpr (VPL == 4)
+      *reinterpret_cast<uint2*>(out + oi) = *reinterpret_cast<const uint2*>(vals);
+    else
+      *reinterpret_cast<uint4*>(out + oi) = *reinterpret_cast<const uint4*>(vals);
   }
   MSGL_TRD(9, clock64());      // merged rows written
   MSGL_TRD(10, trace_wall());

@@ -78,12 +78,14 @@ struct TcShape {
   static constexpr int kCtasPerSm = (NSUB == 2 || HD == 256) ? 1 : 2;
   // register cap at launch: the one-sub-tile shapes start at 80 registers either way (the
   // setmaxnreg budgets below are written against that pool)
-  static constexpr int kMinCtasForRegs = NSUB == 2 ? 1 : 2;
+  // (head_dim 256 runs one CTA per SM anyway: its per-token form takes the larger cap, 168
+  // registers for every warp, instead of spilling under 80)
+  static constexpr int kMinCtasForRegs = (NSUB == 2 || (HD == 256 && !PAGED)) ? 1 : 2;
   // The CTA's register pool is threads x registers at launch; setmaxnreg moves registers between
   // the softmax warps and the others inside that pool.  The PAGED one-sub-tile shape (256 threads
   // at 128 registers, two CTAs per SM = the whole register file) already gives its softmax warps
   // what they need: no re-balancing there.
-  static constexpr bool kRebalanceRegs = !(PAGED && NSUB == 1);
+  static constexpr bool kRebalanceRegs = !(PAGED && NSUB == 1) && !(HD == 256 && !PAGED);
 };
 
 // ---------------------------------------------------------------- PTX wrappers

@@ -246,6 +246,28 @@ def cfg5a_decode(seed: int = 505, device="cuda", batch: int = 256, lo: int = 409
                        num_kv_splits=num_kv_splits, max_kv_splits=max_kv_splits)
 
 
+def d256_prefill_point(hkv: int, hq: int, q_len: int, prefix: int = 0, seed: int = 707,
+                       device="cuda") -> Workload:
+    """head_dim 256, one sequence of ``q_len`` new tokens after ``prefix`` cached ones, causal:
+    the shapes of the reference's own prefill sweep (head configurations (kv, q) = (2, 16),
+    (4, 16), (4, 24), (2, 32); mini-sglang-mlx-kernel/test_and_bench/paged_prefill_attention.py:20-26, 329-331)."""
+    pages = (q_len + prefix + PAGE_SIZE - 1) // PAGE_SIZE
+    return make_prefill(f"d256_prefill_kv{hkv}_q{hq}_t{q_len}_p{prefix}", hq=hq, hkv=hkv,
+                        q_lens=[q_len], prefix_lens=[prefix], num_pages=pages + pages // 4 + 16,
+                        seed=seed + q_len + prefix, device=device, head_dim=256)
+
+
+def d256_decode_point(hkv: int, hq: int, kv_len: int, batch: int = 1, seed: int = 808,
+                      device="cuda") -> Workload:
+    """head_dim 256 decode over ``batch`` sequences of ``kv_len`` tokens: the shapes of the
+    reference's own decode sweep (single sequences and uniform batches;
+    mini-sglang-mlx-kernel/test_and_bench/paged_decode_attention.py:18-23, 241-257)."""
+    pages = batch * ((kv_len + PAGE_SIZE - 1) // PAGE_SIZE)
+    return make_decode(f"d256_decode_kv{hkv}_q{hq}_l{kv_len}_b{batch}", hq=hq, hkv=hkv,
+                       kv_lens=[kv_len] * batch, num_pages=pages + pages // 4 + 16,
+                       seed=seed + kv_len + batch, device=device, head_dim=256)
+
+
 CFG5B_CHUNKS = (128, 256, 512, 1024, 2048, 4096)
 CFG5B_PREFIXES = (1024, 2048, 4096, 8192, 16384, 32768)
 

@@ -94,6 +94,28 @@ def test_prefill_rejects_bad_arguments(kw, code, text):
     assert text in _lib.last_error()
 
 
+def test_attention_ops_reject_misaligned_tensors():
+    """Pointers are only compared here, never followed: the check comes before any CUDA call."""
+    lib = _lib.lib()
+    ok, odd = 0x10000, 0x10008
+    assert lib.msgl_paged_decode_attention(odd, ok, ok, ok, ok, None, ok, ok, 1 << 20, 2, 16, 8, 128, 64,
+                                           0, 0.1, 4, None) == 5
+    assert "16-byte aligned" in _lib.last_error()
+    assert lib.msgl_paged_prefill_attention(ok, ok, odd, ok, ok, ok, ok, ok, ok, 1 << 20, 2, 8, 100, 32, 8,
+                                            128, 64, 0, 0.1, 4, 0, 0, None) == 5
+    assert "16-byte aligned" in _lib.last_error()
+
+
+def test_prefill_launch_count_is_host_arithmetic():
+    lib = _lib.lib()
+    # a 512-token chunk per sequence fills the GPU with query tiles: one launch
+    assert lib.msgl_prefill_launch_count(4, 2048, 16000, 32, 8, 128, 512, 0, 1) == 1
+    # 128 query tokens over 32768 keys: split in many pieces of 256 rows, merged by a second launch
+    assert lib.msgl_prefill_launch_count(1, 128, 32896, 32, 8, 128, 128, 0, 1) == 2
+    # a 16-token draft block over a window: small units, merged inside the launch
+    assert lib.msgl_prefill_launch_count(16, 256, 16 * 8192, 32, 8, 128, 16, 4096, 1) == 1
+
+
 def test_store_rejects_bad_arguments():
     lib = _lib.lib()
     assert lib.msgl_store_kv_cache(None, None, None, None, None, 4, 8, 126, 64, 8 * 126, 8 * 126, 0, None, None) == 1
