@@ -245,12 +245,12 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
     chunk = (chunk + 127) / 128 * 128;
     if (chunk < visible) pl.kv_chunk = static_cast<int>(chunk);
     // One CTA merges a unit at the pace of one SM's L2 port (about 17 GB/s measured with the
-    // rows of the other splits in flight): fine for the draft-block and verify units (tens of
-    // KB, a few us, and no second launch), not for a 256-row unit of many pieces (128 query
-    // tokens over 32768 keys: 9 x 256 rows x 512 B = 1.2 MB, 70 us against 4 us spread over the
-    // grid of a second launch).
+    // rows of the other splits in flight): fine for the draft-block and verify units (64 rows x 2
+    // pieces x 512 B = 64 KB, a few us, and no second launch), not for a 256-row unit (chunk 512
+    // in 2 pieces: 256 KB, 15 us; 128 query tokens over 32768 keys in 9 pieces: 1.2 MB, 70 us
+    // against 4 us spread over the grid of a second launch).
     const int64_t rows = std::min<int64_t>(BM, static_cast<int64_t>(max_len_extend) * G);
-    pl.fused_merge = pieces * rows * head_dim * 4 <= 256 * 1024;
+    pl.fused_merge = pieces * rows * head_dim * 4 <= 64 * 1024;
   }
 #ifdef MSGL_TRACE
   // development builds only: a key-range piece length to try instead of the policy's
