@@ -156,6 +156,15 @@ int msgl_paged_decode_attention_static(
 int msgl_read_status(void* workspace, int clear, int* status_out, void* stream);
 
 /*
+ * Self-test of the bounded waits: launches one small CTA whose warps wait, the way the
+ * attention kernels do, on a barrier that nothing completes; the wait gives up after about
+ * limit_us microseconds (1 .. 100000), the kernel sets the status word of `workspace` to 1
+ * and returns, and the context stays usable.  Read the result with msgl_read_status.  For
+ * deployment checks and tests; no counterpart in the reference.
+ */
+int msgl_selftest_bounded_wait(void* workspace, int limit_us, void* stream);
+
+/*
  * msgl_paged_decode_attention with the output gate of the reference's Qwen3.5 attention
  * layer fused into the final write: out = attention * sigmoid(gate), gate (batch,
  * num_q_heads, head_dim) in the data dtype, both factors rounded to that dtype before the

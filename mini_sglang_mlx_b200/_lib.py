@@ -36,6 +36,7 @@ SIGNATURES = {
         _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _f, _i, _vp]),
     "msgl_read_status": (_i, [_vp, _i, _vp, _vp]),
     "msgl_prefill_workspace_bytes": (_sz, [_i, _i, _i64, _i, _i, _i, _i, _i]),
+    "msgl_selftest_bounded_wait": (_i, [_vp, _i, _vp]),
     "msgl_prefill_launch_count": (_i, [_i, _i, _i64, _i, _i, _i, _i, _i, _i]),
     "msgl_page_index_workspace_bytes": (_sz, [_i, _i64, _i]),
     "msgl_paged_decode_attention_p16": (

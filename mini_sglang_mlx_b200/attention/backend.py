@@ -221,21 +221,26 @@ class AttnBackend:
         if not self._staging or self._staging[0].numel() < 3 * n:
             cap = max(64, 1 << max(n - 1, 0).bit_length())
             self._staging = [torch.empty(3 * cap, dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._staging_np = [t.numpy() for t in self._staging]   # same memory, cheap row writes
             self._staging_events = [torch.cuda.Event() for _ in range(4)]
             self._staging_next = 0
         k = self._staging_next
         self._staging_next = (k + 1) % len(self._staging)
         self._staging_events[k].synchronize()
         req = self._staging[k][: 3 * n].view(3, n)
-        req.copy_(torch.tensor([list(extend_lens), list(kv_lens), list(rows)], dtype=torch.int32))
+        rows_np = self._staging_np[k][: 3 * n].reshape(3, n)
+        rows_np[0] = extend_lens
+        rows_np[1] = kv_lens
+        rows_np[2] = rows
         return req, self._staging_events[k]
 
     def _index_arrays(self, reqs, extend_lens: Sequence[int], kv_lens: Sequence[int], split_chunk: int):
         req, event = self._stage(extend_lens, kv_lens, [r.table_idx for r in reqs])
+        ps = self.page_size if self._paged_ops else 1
         md = build_attn_metadata(req, self.page_table, total_q=sum(extend_lens), total_kv=sum(kv_lens),
-                                 page_size=self.page_size if self._paged_ops else 1,
-                                 split_chunk=split_chunk, max_kv_splits=MAX_KV_SPLITS,
-                                 per_token_ids=not self._paged_ops)
+                                 page_size=ps, split_chunk=split_chunk, max_kv_splits=MAX_KV_SPLITS,
+                                 per_token_ids=not self._paged_ops,
+                                 total_pages=sum((l + ps - 1) // ps for l in kv_lens) if ps > 1 else 0)
         event.record()
         return md
 

@@ -269,6 +269,27 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
   return pl;
 }
 
+// The waiting pattern of the attention kernels on a barrier that nothing completes: two warps wait
+// (bounded), the first to run out raises the CTA's abort flag, the other sees it and leaves too,
+// the status word gets 1 and the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    msgl::mbar_init(msgl::smem_u32(&bar), 1);
+    msgl::fence_mbar_init();
+  }
+  __syncthreads();
+  // the second warp gets a far longer limit: it must leave through the abort flag
+  const long long limit = threadIdx.x < 32 ? limit_cycles : limit_cycles * 1000;
+  const bool ok = msgl::mbar_wait_limit(msgl::smem_u32(&bar), 0, &s_abort, limit);
+  const bool all_out = __all_sync(0xffffffffu, !ok);
+  __syncthreads();
+  if (threadIdx.x == 0) msgl::mbar_inval(msgl::smem_u32(&bar));
+  if (all_out && (threadIdx.x & 31) == 0) atomicExch(status, 1);
+}
+
 // ---- small data-movement kernels
 template <int VEC_BYTES>
 __global__ void store_kv_kernel(unsigned char* __restrict__ kc, unsigned char* __restrict__ vc,
@@ -697,6 +718,18 @@ int msgl_read_status(void* workspace, int clear, int* status_out, void* stream) 
                   ? "read_status: a slot or page id outside the pool, or a length beyond a sequence's "
                     "pages, was met (those rows were read as zeros)"
                   : "read_status: unknown device status " + std::to_string(value));
+}
+
+int msgl_selftest_bounded_wait(void* workspace, int limit_us, void* stream) {
+  if (!workspace) return fail(MSGL_BAD_ARG, "selftest_bounded_wait: null workspace");
+  if (limit_us < 1 || limit_us > 100000)
+    return fail(MSGL_BAD_ARG, "selftest_bounded_wait: limit_us must be in [1, 100000]");
+  // about 2 cycles per nanosecond: the wait gives up after limit_us at the latest
+  bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<int*>(workspace), static_cast<long long>(limit_us) * 2000);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("selftest_bounded_wait", e);
+  return MSGL_OK;
 }
 
 size_t msgl_prefill_workspace_bytes(int batch, int total_q, int64_t total_kv, int num_q_heads,

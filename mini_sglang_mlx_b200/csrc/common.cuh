@@ -202,17 +202,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// Bounded wait: false after kTcWaitCycles or once another thread has given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait: false after `limit` SM cycles or once another thread has given up.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag != 0 || clock64() - t0 > kTcWaitCycles) {
+    if (*abort_flag != 0 || clock64() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, kTcWaitCycles);
 }
 // Warp-uniform form: every lane waits, the warp agrees on the outcome, so that the
 // warp-collective instructions that follow are executed by all lanes or by none.

@@ -39,12 +39,38 @@ _workspaces: Dict[Tuple[int, int, str], torch.Tensor] = {}
 _retired: list = []   # outgrown buffers stay alive: work queued on their stream may still use them
 
 
+_raw_current_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_handle(stream, device: torch.device) -> int:
     if stream is None:
+        # (the raw getter skips the construction of a Stream object: a few microseconds per call)
+        if _raw_current_stream is not None:
+            return _raw_current_stream(device.index if device.index is not None
+                                       else torch.cuda.current_device())
         return torch.cuda.current_stream(device).cuda_stream
     if isinstance(stream, torch.cuda.Stream):
         return stream.cuda_stream
     return int(stream)
+
+
+class _NoCtx:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_CTX = _NoCtx()
+
+
+def _on_device(device: torch.device):
+    """Context that makes ``device`` current for the launches inside; nothing to do (and nothing
+    to pay) when it already is."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_CTX
+    return torch.cuda.device(device)
 
 
 def _workspace(nbytes: int, device: torch.device, stream_handle: int, kind: str) -> torch.Tensor:
@@ -127,7 +153,7 @@ def paged_decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, num_kv_sp
     out = torch.empty_like(q)
     sh = _stream_handle(stream, q.device)
     lib = _lib.lib()
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         need = lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits))
         ws = _workspace(need, q.device, sh, "decode")
         tail = (out.data_ptr(), ws.data_ptr(), ws.numel(), batch, hq, k_cache.shape[1], d,
@@ -169,7 +195,7 @@ def paged_prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indice
     sh = _stream_handle(stream, q.device)
     lib = _lib.lib()
     total_kv = kv_indices.numel()
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         need = lib.msgl_prefill_workspace_bytes(batch, total_q, total_kv, hq, k_cache.shape[1], d,
                                                 int(max_len_extend), int(sliding_window_size))
         ws = _workspace(need, q.device, sh, "prefill")
@@ -209,7 +235,7 @@ def paged_decode_attention_p16(q, k_cache, v_cache, page_indptr, page_indices, k
     sh = _stream_handle(stream, q.device)
     lib = _lib.lib()
     total_pages = page_indices.numel()
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         need = ((lib.msgl_decode_workspace_bytes(batch, hq, d, int(max_kv_splits)) + 255) // 256 * 256
                 + lib.msgl_page_index_workspace_bytes(batch, total_pages, int(page_size)))
         ws = _workspace(need, q.device, sh, "decode")
@@ -246,7 +272,7 @@ def paged_prefill_attention_p16(q, k_cache, v_cache, qo_indptr, page_indptr, pag
     sh = _stream_handle(stream, q.device)
     lib = _lib.lib()
     total_pages = page_indices.numel()
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         need = lib.msgl_prefill_workspace_bytes_p16(batch, total_q, total_pages, int(page_size), hq,
                                                     k_cache.shape[1], d, int(max_len_extend),
                                                     int(sliding_window_size))
@@ -293,7 +319,7 @@ def store_kv_cache(k_cache, v_cache, indices, k, v, *, stream=None) -> None:
              f"{op}: k/v (and the two caches) must share their row stride")
     _require(indices.is_contiguous(), f"{op}: indices must be contiguous")
     sh = _stream_handle(stream, k_cache.device)
-    with torch.cuda.device(k_cache.device):
+    with _on_device(k_cache.device):
         status = _workspace(256, k_cache.device, sh, "decode")   # dropped rows are reported there
         _lib.check(_lib.lib().msgl_store_kv_cache(
             k_cache.data_ptr(), v_cache.data_ptr(), indices.data_ptr(), k.data_ptr(), v.data_ptr(),
@@ -339,7 +365,7 @@ def qk_norm_rope_store(q, k, v, q_weight, k_weight, positions, out_loc, k_cache,
              f"{op}: tensors must live on the same CUDA device")
     rd = d if rotary_dim is None else int(rotary_dim)
     sh = _stream_handle(stream, q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _lib.check(_lib.lib().msgl_qk_norm_rope_store(
             q.data_ptr(), k.data_ptr(), v.data_ptr(),
             q_weight.data_ptr() if q_weight is not None else None,
@@ -366,7 +392,7 @@ def gather_kv_indices(page_table, table_idx, kv_indptr, total_kv: int, *, stream
     _require(kv_indptr.numel() == batch + 1, f"{op}: kv_indptr must have batch+1 entries")
     out = torch.empty(int(total_kv), dtype=torch.int32, device=page_table.device)
     sh = _stream_handle(stream, page_table.device)
-    with torch.cuda.device(page_table.device):
+    with _on_device(page_table.device):
         status = _workspace(256, page_table.device, sh, "decode")
         _lib.check(_lib.lib().msgl_gather_kv_indices(
             page_table.data_ptr(), page_table.stride(0), table_idx.contiguous().data_ptr(),
@@ -377,7 +403,7 @@ def gather_kv_indices(page_table, table_idx, kv_indptr, total_kv: int, *, stream
 
 def build_attn_metadata(req_host: torch.Tensor, page_table: torch.Tensor, *, total_q: int, total_kv: int,
                         page_size: int = 1, split_chunk: int = 0, max_kv_splits: int = 32,
-                        per_token_ids: bool = True, stream=None):
+                        per_token_ids: bool = True, total_pages: int = None, stream=None):
     """Every index array of a step from the device page table with ONE host-to-device copy and
     ONE launch.  ``req_host``: (3, batch) int32 on the host (pinned for a copy that does not
     block): new tokens, KV lengths, page-table rows.  Returns a dict of int32 device views into
@@ -394,14 +420,20 @@ def build_attn_metadata(req_host: torch.Tensor, page_table: torch.Tensor, *, tot
     dev = page_table.device
     batch = req_host.shape[1]
     paged = int(page_size) > 1
-    total_pages = int((req_host[1].to(torch.int64) + page_size - 1).div(page_size, rounding_mode="floor").sum()) \
-        if paged else 0
+    if not paged:
+        total_pages = 0
+    elif total_pages is None:   # (the caller usually knows it: pass it and save the host pass)
+        kv = req_host.numpy()[1].astype("int64")
+        total_pages = int(((kv + (page_size - 1)) // page_size).sum())
     sizes = dict(req=3 * batch, qo_indptr=batch + 1, kv_indptr=batch + 1, prefix_lens=batch,
                  num_kv_splits=batch, positions=int(total_q),
                  kv_indices=int(total_kv) if per_token_ids else 0,
                  page_indptr=batch + 1 if paged else 0, page_indices=total_pages)
     sh = _stream_handle(stream, dev)
-    with torch.cuda.device(dev), torch.cuda.stream(torch.cuda.ExternalStream(sh, device=dev)):
+    # the buffer is allocated and filled on the stream the kernel runs on; with the current stream
+    # (the usual call) that needs no stream context
+    stream_ctx = _NO_CTX if stream is None else torch.cuda.stream(torch.cuda.ExternalStream(sh, device=dev))
+    with _on_device(dev), stream_ctx:
         buf = torch.empty(sum(sizes.values()), dtype=torch.int32, device=dev)
         out, off = {}, 0
         for name, n in sizes.items():

@@ -309,3 +309,30 @@ def test_metadata_kernel_reports_rows_and_lengths_outside_the_table():
                 [[30, 1], [10, 40], [1, 3]]):        # more new tokens than tokens
         build_attn_metadata(torch.tensor(bad, dtype=torch.int32), table, total_q=64, total_kv=128)
         assert device_status() == 2
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_survives():
+    """The waits of the attention kernels give up after a limit, raise the CTA's abort flag, set
+    the status word to 1 and let the kernel return.  The self-test entry point runs that pattern
+    on a barrier nothing completes (limit 200 us here); afterwards the status reads 1 with the
+    message of the condition, clears, and the same stream runs an operator correctly."""
+    import ctypes
+    from mini_sglang_mlx_b200 import _lib, store_kv_cache
+    lib = _lib.lib()
+    dev = torch.device("cuda")
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.msgl_selftest_bounded_wait(ws.data_ptr(), 200, stream) == 0
+    word = ctypes.c_int(-1)
+    assert lib.msgl_read_status(ws.data_ptr(), 1, ctypes.byref(word), stream) == 7
+    assert word.value == 1 and "bounded wait" in _lib.last_error()
+    assert lib.msgl_read_status(ws.data_ptr(), 0, ctypes.byref(word), stream) == 0 and word.value == 0
+    assert lib.msgl_selftest_bounded_wait(None, 200, stream) == 5
+    # the context is intact
+    kc = torch.zeros(8, 2, 128, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    k = torch.randn(3, 2, 128, device=dev).bfloat16()
+    idx = torch.tensor([5, 0, 2], dtype=torch.int32, device=dev)
+    store_kv_cache(kc, vc, idx, k, k)
+    torch.cuda.synchronize()
+    assert torch.equal(kc[idx.long()], k)
