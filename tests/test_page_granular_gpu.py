@@ -188,16 +188,21 @@ def test_cfg5a_reduced_against_the_oracle_and_the_per_token_op():
 
 def test_cfg5a_full_size_properties():
     """The long-context decode batch at full size (38 GB of K/V) through the page-granular entry:
-    split-count invariance, exact doubling with V, and three sequences against the oracle."""
-    from mini_sglang_mlx_b200 import synthetic as S
+    split-count invariance, exact doubling with V, 16 of the 256 sequences (evenly spaced in the
+    order of their lengths) against the oracle, and all 256 against the per-token operator."""
+    from mini_sglang_mlx_b200 import paged_decode_attention, synthetic as S
     from mini_sglang_mlx_b200.attention import compute_num_kv_splits
     w = S.cfg5a_decode()
     tuned = torch.tensor(compute_num_kv_splits(w.kv_lens, w.hkv), dtype=torch.int32).cuda()
     out = _run_paged(w, tuned)
     assert torch.isfinite(out.float()).all()
     assert (out.float() - _run_paged(w).float()).abs().max() <= 1.6e-2
+    per_token = paged_decode_attention(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, tuned,
+                                       w.sm_scale, w.max_kv_splits)
+    assert (out.float() - per_token.float()).abs().max() <= 1.6e-2
+    del per_token
     order = sorted(range(w.batch), key=lambda b: w.kv_lens[b])
-    pick = [order[0], order[len(order) // 2], order[-1]]
+    pick = sorted({order[round(i * (len(order) - 1) / 15)] for i in range(16)})
     ref = _oracle_for(w, seqs=pick)
     assert_close_to_oracle(out[pick], ref[pick], "cfg5a full size, page-granular, subsample")
     w.v_cache.mul_(2)
