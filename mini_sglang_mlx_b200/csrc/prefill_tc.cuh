@@ -1143,8 +1143,9 @@ __global__ void __launch_bounds__(TcShape<NSUB, HD, PAGED>::kThreads,
     if (s_last != 0 && warp < kMergers) {
       // the softmax warps merge (a function of its own: its registers do not weigh on the main loop)
       const MergeArgs ma{p.part_o, p.part_ml, p.out, p.gate, p.hq, p.group};
-      // (2 rows x 2 splits in flight per lane: what the register cap of the main kernel holds)
-      merge_kv_splits<T, HD, kMergers, BM, 2, 2>(ma, nsp, slot0, p.hkv, 0, rows_valid,
+      // (rows x 2 splits in flight per lane: what the register cap of the main kernel holds)
+      constexpr int kMergeRows = (!Shape::kRebalanceRegs && HD == 128) ? 4 : 2;
+      merge_kv_splits<T, HD, kMergers, BM, kMergeRows, 2>(ma, nsp, slot0, p.hkv, 0, rows_valid,
                                                                     pk0, sq.q_begin, h);
 #ifdef MSGL_TRACE
       if (tid == 0) MSGL_TR(14, clock64());
