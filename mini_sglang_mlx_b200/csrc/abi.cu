@@ -249,8 +249,10 @@ PrefillPlan plan_prefill(int batch, int total_q, int64_t total_kv, int hq, int h
     // pieces x 512 B = 64 KB, a few us, and no second launch), not for a 256-row unit (chunk 512
     // in 2 pieces: 256 KB, 15 us; 128 query tokens over 32768 keys in 9 pieces: 1.2 MB, 70 us
     // against 4 us spread over the grid of a second launch).
+    // (sized for a sequence of average length: the lengths themselves are device data)
     const int64_t rows = std::min<int64_t>(BM, static_cast<int64_t>(max_len_extend) * G);
-    pl.fused_merge = pieces * rows * head_dim * 4 <= 64 * 1024;
+    const int64_t pieces_used = (visible / batch + chunk - 1) / chunk;
+    pl.fused_merge = pieces_used * rows * head_dim * 4 <= 64 * 1024;
   }
 #ifdef MSGL_TRACE
   // development builds only: a key-range piece length to try instead of the policy's

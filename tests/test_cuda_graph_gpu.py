@@ -53,12 +53,18 @@ def test_decode_replays_on_new_contents():
                                f"decode graph replay {seed}")
 
 
-@pytest.mark.parametrize("q_lens,prefix", [([64, 200], [100, 0]), ([8, 8], [3000, 5000])], ids=str)
+@pytest.mark.parametrize("q_lens,prefix", [([64, 200], [100, 0]), ([8, 8], [3000, 5000]), ([128], [20000])],
+                         ids=str)
 def test_prefill_replays_on_new_contents(q_lens, prefix):
-    from mini_sglang_mlx_b200 import paged_prefill_attention
+    """Unsplit, split with the merge inside the launch, and split with the merge as a second,
+    programmatically dependent launch (both launches are captured)."""
+    from mini_sglang_mlx_b200 import _lib, paged_prefill_attention
     g = torch.Generator().manual_seed(5)
     hkv, hq, d = 2, 8, 128
     kv_lens = [p + t for p, t in zip(prefix, q_lens)]
+    launches = _lib.lib().msgl_prefill_launch_count(len(q_lens), sum(q_lens), sum(kv_lens), hq, hkv, d,
+                                                    max(q_lens), 0, 0)
+    assert launches == (2 if q_lens == [128] else 1)
     total = sum(kv_lens)
     kc = torch.randn(total + 9, hkv, d, generator=g).bfloat16().cuda()
     vc = torch.randn(total + 9, hkv, d, generator=g).bfloat16().cuda()
