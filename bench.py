@@ -620,18 +620,30 @@ def measure(name, device, rank, world, steps, warmup, dist_on, flush, peaks, pea
 
 
 # ----------------------------------------------------------------------------- strong scaling
+LAST_STEP_STATS = {}
+
+
 def _timed_steps(call, steps, dist_on):
-    """Device time (ms) of `steps` calls in a row, max over ranks."""
+    """Device time (ms) per call over `steps` calls in a row: the MEDIAN step of each rank, max
+    over ranks.  The mean and the slowest single step (each the max over ranks) are left in
+    LAST_STEP_STATS: with eight processes on a shared host a rank now and then stalls for tens of
+    milliseconds between two launches (seen: one 26 ms step among twenty of 0.67 ms), which the
+    mean of a 20-step run of a sub-millisecond step shows and the median does not."""
     for _ in range(3):
         call()
     barrier(dist_on)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    marks[0].record()
+    for i in range(steps):
         out = call()
-    end.record()
+        marks[i + 1].record()
     barrier(dist_on)
-    return max_over_ranks(start.elapsed_time(end), dist_on) / steps, out
+    per = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+    LAST_STEP_STATS.clear()
+    LAST_STEP_STATS.update(timing="median step of each rank, max over ranks",
+                           mean_ms=max_over_ranks(marks[0].elapsed_time(marks[steps]), dist_on) / steps,
+                           slowest_step_ms=max_over_ranks(per[-1], dist_on))
+    return max_over_ranks(per[len(per) // 2], dist_on), out
 
 
 def sharded_decode(device, rank, world, steps):
@@ -680,6 +692,7 @@ def sharded_decode(device, rank, world, steps):
 
     call = lambda: paged_decode_attention_p16(q, kc, vc, pip, pidx, lens, splits, 1 / math.sqrt(128), 32)  # noqa: E731
     ms, out_local = _timed_steps(call, steps, True)
+    step_stats = dict(LAST_STEP_STATS)
     plan = P.GatherPlan(shards, [1] * batch, device)
     gather = lambda: P.gather_request_outputs(out_local, plan)  # noqa: E731
     gms, full_out = _timed_steps(gather, 3, True)
@@ -687,7 +700,7 @@ def sharded_decode(device, rank, world, steps):
     return {"workload": name, "split": "by request: parallel.assign_requests, longest first onto the "
                                        "least loaded rank; per-rank pool, page index and lengths",
             "scaling": "strong", "value": total_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
-            "ms_per_step": ms, "reassembly_ms": gms,
+            "ms_per_step": ms, **step_stats, "reassembly_ms": gms,
             "value_with_reassembly": total_bytes / ((ms + gms) * 1e-3) / 1e9,
             "load_imbalance_max_over_mean": max(rank_bytes) / (sum(rank_bytes) / world),
             "sequences_per_rank": [len(s) for s in shards],
@@ -713,13 +726,14 @@ def sharded_by_head(device, rank, world, steps):
         return paged_prefill_attention_p16(q_, kc_, vc_, w.qo_indptr, pip, pidx, lens, w.prefix_lens,
                                            w.sm_scale, w.max_len_extend)
     ms, out_local = _timed_steps(lambda: run(q, kc, vc), steps, True)
+    step_stats = dict(LAST_STEP_STATS)
     gms, full_out = _timed_steps(lambda: P.gather_head_outputs(out_local), 3, True)
     err = None
     if rank == 0:
         err = float((full_out.float() - run(w.q, w.k_cache, w.v_cache).float()).abs().max())
     flops = w.algorithmic_flops()
     return {"workload": w.name, "split": "by KV-head group: parallel.head_slices", "scaling": "strong",
-            "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+            "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, **step_stats,
             "reassembly_ms": gms, "value_with_reassembly": flops / ((ms + gms) * 1e-3) / 1e12,
             "max_abs_diff_to_unsharded": err, "tolerance": 2e-2, "steps": steps}
 
