@@ -321,3 +321,18 @@ def test_mask_known_answers_through_the_page_entry():
         want = torch.tensor(case["expected_weights"], dtype=torch.float32)
         got = out.float().cpu()[:, 0, : d["kv_len"]]
         assert torch.allclose(got, want, rtol=case["rtol"], atol=case["atol"]), case["name"]
+
+
+def test_prefill_batches_of_more_than_128_sequences():
+    """The work-item scan of large batches (natural order, no sorting) on the page-granular path,
+    unsplit and with the key range split."""
+    import numpy as np
+    from mini_sglang_mlx_b200 import synthetic as S
+    rng = np.random.default_rng(12)
+    for hkv, hq, kv_hi in ((2, 8, 700), (1, 4, 5000)):
+        q_lens = rng.integers(1, 9, size=140).tolist()
+        prefixes = rng.integers(0, kv_hi, size=140).tolist()
+        pages = sum((a + b + 15) // 16 for a, b in zip(q_lens, prefixes))
+        w = S.make_prefill("large_batch", hq=hq, hkv=hkv, q_lens=q_lens, prefix_lens=prefixes,
+                           num_pages=pages + 32, seed=77 + hkv, device="cuda")
+        assert_close_to_oracle(_run_paged(w), _oracle_for(w), f"140 sequences, kv up to {kv_hi}")

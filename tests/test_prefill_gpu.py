@@ -235,3 +235,18 @@ def test_cfg5b_largest_point_properties():
         assert_close_to_oracle(out[first:first + n], ref, f"cfg5b 4096x32768 rows {first}..")
     w.v_cache.mul_(2)
     assert torch.equal(_run_workload(w), out * 2)
+
+
+@pytest.mark.parametrize("hkv,hq,kv_hi", [(2, 8, 700), (1, 4, 5000)], ids=["unsplit", "split"])
+def test_batches_of_more_than_128_sequences(hkv, hq, kv_hi):
+    """Above 128 sequences the CTAs find their work item by a running scan in the natural order
+    instead of the sorted search; (1, 4): few enough query tiles for the key range to be split
+    (two launches or arrival counters), (2, 8): unsplit.  Ragged lengths, some sequences without
+    query tokens."""
+    rng = np.random.default_rng(11)
+    batch = 140
+    q_lens = rng.integers(0, 9, size=batch).tolist()
+    q_lens[3] = 8
+    prefixes = rng.integers(0, kv_hi, size=batch).tolist()
+    d = make_inputs(q_lens, prefixes, hkv, hq, seed=41)
+    assert_close_to_oracle(run(d), oracle(d), f"batch of {batch}, kv up to {kv_hi}")
