@@ -336,3 +336,24 @@ def test_prefill_batches_of_more_than_128_sequences():
         w = S.make_prefill("large_batch", hq=hq, hkv=hkv, q_lens=q_lens, prefix_lens=prefixes,
                            num_pages=pages + 32, seed=77 + hkv, device="cuda")
         assert_close_to_oracle(_run_paged(w), _oracle_for(w), f"140 sequences, kv up to {kv_hi}")
+
+
+@pytest.mark.parametrize("hkv,hq", [(4, 24), (2, 24), (1, 1), (2, 32), (3, 15)], ids=str)
+def test_prefill_head_ratios(hkv, hq):
+    """Query heads per KV head that divide 128 (the query tile arrives as TMA boxes) and that do
+    not (6, 12, 5: 16-byte copies by the producer warps), short and long query blocks."""
+    from mini_sglang_mlx_b200 import synthetic as S
+    for q_lens, prefixes in (([8, 3], [700, 2500]), ([300, 77], [100, 0])):
+        pages = sum((a + b + 15) // 16 for a, b in zip(q_lens, prefixes))
+        w = S.make_prefill("heads", hq=hq, hkv=hkv, q_lens=q_lens, prefix_lens=prefixes,
+                           num_pages=pages + 8, seed=5 + hq, device="cuda")
+        assert_close_to_oracle(_run_paged(w), _oracle_for(w), f"heads ({hkv}, {hq}) q {q_lens}")
+
+
+@pytest.mark.parametrize("hkv,hq", [(4, 24), (1, 1), (2, 32), (3, 15)], ids=str)
+def test_decode_head_ratios(hkv, hq):
+    from mini_sglang_mlx_b200 import synthetic as S
+    kv_lens = [1, 700, 2500, 33]
+    pages = sum((l + 15) // 16 for l in kv_lens)
+    w = S.make_decode("heads", hq=hq, hkv=hkv, kv_lens=kv_lens, num_pages=pages + 8, seed=9 + hq, device="cuda")
+    assert_close_to_oracle(_run_paged(w), _oracle_for(w), f"decode heads ({hkv}, {hq})")
