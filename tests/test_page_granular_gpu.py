@@ -38,7 +38,7 @@ def make_pool(kv_lens, page_size, hkv, *, seed=0, d=128, spare_pages=5, dtype=to
     return kc, vc, page_indptr.cuda(), page_indices.cuda(), slots.cuda()
 
 
-@pytest.mark.parametrize("page_size", [1, 16, 32, 64])
+@pytest.mark.parametrize("page_size", [1, 16, 32, 48, 64])
 @pytest.mark.parametrize("kv_lens", [[1], [237, 809], [16, 32, 48], [0, 5, 0, 4097], [2048] * 3 + [1],
                                      [15, 17, 63, 65, 1023, 1025]], ids=str)
 def test_decode_matches_the_per_token_op_and_the_oracle(page_size, kv_lens):
@@ -59,7 +59,7 @@ def test_decode_matches_the_per_token_op_and_the_oracle(page_size, kv_lens):
     assert_close_to_oracle(out, ref, f"decode p{page_size} {kv_lens}")
 
 
-@pytest.mark.parametrize("page_size", [1, 16, 32])
+@pytest.mark.parametrize("page_size", [1, 16, 32, 48])
 @pytest.mark.parametrize("case", [
     dict(q_lens=[5, 17], prefix=[0, 40]),
     dict(q_lens=[1, 16, 15, 17], prefix=[0, 0, 1, 47]),
@@ -357,3 +357,23 @@ def test_decode_head_ratios(hkv, hq):
     pages = sum((l + 15) // 16 for l in kv_lens)
     w = S.make_decode("heads", hq=hq, hkv=hkv, kv_lens=kv_lens, num_pages=pages + 8, seed=9 + hq, device="cuda")
     assert_close_to_oracle(_run_paged(w), _oracle_for(w), f"decode heads ({hkv}, {hq})")
+
+
+def test_decode_split_hints_do_not_change_the_result():
+    """1, 7, 32 and 128 splits per sequence (the workspace layout's maximum) on the page-granular
+    path: the same rows up to fp32 rounding, and the oracle's."""
+    from mini_sglang_mlx_b200 import paged_decode_attention_p16, synthetic as S
+    kv_lens = [40000, 513, 16, 9000]
+    pages = sum((l + 15) // 16 for l in kv_lens)
+    w = S.make_decode("hints", hq=16, hkv=4, kv_lens=kv_lens, num_pages=pages + 8, seed=21, device="cuda")
+    pip, pidx, lens = w.page_csr()
+    ref = _oracle_for(w)
+    outs = []
+    for hint, mx in ((1, 32), (7, 8), (32, 32), (128, 128)):
+        splits = torch.full((len(kv_lens),), hint, dtype=torch.int32, device="cuda")
+        out = paged_decode_attention_p16(w.q, w.k_cache, w.v_cache, pip, pidx, lens, splits, w.sm_scale, mx)
+        torch.cuda.synchronize()
+        assert_close_to_oracle(out, ref, f"decode with {hint} splits")
+        outs.append(out.float())
+    for o in outs[1:]:
+        assert (o - outs[0]).abs().max().item() <= 1.6e-2
