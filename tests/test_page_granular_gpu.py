@@ -70,6 +70,7 @@ def test_decode_matches_the_per_token_op_and_the_oracle(page_size, kv_lens):
     dict(q_lens=[16] * 4, prefix=[3000, 100, 0, 2047], window=1024),
     dict(q_lens=[8, 8], prefix=[4000, 6000]),                       # short block: key range is split
     dict(q_lens=[33, 1], prefix=[64, 64], cross=True),
+    dict(q_lens=[0, 9, 0, 4], prefix=[50, 0, 0, 700]),              # sequences without query tokens / keys
 ], ids=str)
 def test_prefill_matches_the_per_token_op_and_the_oracle(page_size, case):
     from mini_sglang_mlx_b200 import paged_prefill_attention, paged_prefill_attention_p16
