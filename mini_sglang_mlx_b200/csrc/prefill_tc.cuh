@@ -45,6 +45,13 @@
 // copying warps and the per-token id staging go away.  Only the ragged last page of a sequence
 // (and the pages of a tile past the sequence's end) are filled with 16-byte cp.async copies, so
 // that rows past the sequence's length are zeros rather than whatever the pool holds there.
+//
+// Key-range splits (few query tiles: verify, draft blocks, short chunks over long prefixes): a
+// CTA writes an unnormalised fp32 partial (O rows and their (max, sum)) to scratch; the
+// partials of a (sequence, query tile, head) unit are reduced row by row straight from scratch
+// (merge_kv_splits), either by the CTA that arrives last at the unit's arrival counter, inside
+// the same launch, or -- units whose partials exceed 64 KB -- by prefill_merge_kernel, a second
+// launch chained with programmatic stream serialization that spreads the rows over the grid.
 #pragma once
 
 #include <type_traits>

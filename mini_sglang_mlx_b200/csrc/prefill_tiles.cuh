@@ -1,4 +1,4 @@
-// Work decomposition shared by the paged prefill kernels and their merge pass.
+// Work decomposition shared by the paged prefill kernels and the merge of their key-range splits.
 //
 // Query rows of one sequence and one KV head are "packed": packed index
 // pk = token_local * G + g addresses query token token_local and query head
