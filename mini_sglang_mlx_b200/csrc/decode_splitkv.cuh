@@ -424,7 +424,9 @@ __global__ void __launch_bounds__(NWARPS * 32)
   __syncthreads();
 
   T* out = static_cast<T*>(p.out);
-  for (int g = 0; g < G; ++g) {
+  constexpr int VPL = HD / 32, NV = VPL / 4;   // columns (16-byte pieces) of a row per lane
+  // a warp per query head (heads warp, warp + NWARPS, ...), a lane per VPL consecutive columns
+  for (int g = warp; g < G; g += NWARPS) {
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, sm_m[w * 16 + g]);
@@ -437,21 +439,49 @@ __global__ void __launch_bounds__(NWARPS * 32)
     }
     const float inv = den > 0.f ? 1.f / den : 0.f;
     const int64_t hq_idx = static_cast<int64_t>(b) * p.hq + static_cast<int64_t>(h) * G + g;
-    for (int d = threadIdx.x; d < HD; d += NWARPS * 32) {
-      float num = 0.f;
+    float4 num[NV];
 #pragma unroll
-      for (int w = 0; w < NWARPS; ++w) num += wgt[w] * sm_o[(w * 16 + g) * HD + d];
-      const float val = num * inv;
-      if (splits == 1) {
-        out[hq_idx * HD + d] = p.gate ? apply_gate<T>(val, static_cast<const T*>(p.gate)[hq_idx * HD + d])
-                                      : MmaOp<T>::from_float(val);
-      } else {
-        p.part_o[(hq_idx * p.max_splits + split) * HD + d] = val;
+    for (int e4 = 0; e4 < NV; ++e4) num[e4] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+      const float4* row = reinterpret_cast<const float4*>(sm_o + (w * 16 + g) * HD + lane * VPL);
+#pragma unroll
+      for (int e4 = 0; e4 < NV; ++e4) {
+        const float4 x = row[e4];
+        num[e4].x += wgt[w] * x.x;
+        num[e4].y += wgt[w] * x.y;
+        num[e4].z += wgt[w] * x.z;
+        num[e4].w += wgt[w] * x.w;
       }
     }
-    if (splits > 1 && threadIdx.x == 0) {
-      p.part_lse[hq_idx * p.max_splits + split] =
-          den > 0.f ? M * kLn2 + __logf(den) : -INFINITY;
+#pragma unroll
+    for (int e4 = 0; e4 < NV; ++e4) {
+      num[e4].x *= inv;
+      num[e4].y *= inv;
+      num[e4].z *= inv;
+      num[e4].w *= inv;
+    }
+    if (splits == 1) {
+      const int64_t oi = hq_idx * HD + lane * VPL;
+      alignas(16) T vals[VPL];
+#pragma unroll
+      for (int e4 = 0; e4 < NV; ++e4) {
+        const float f[4] = {num[e4].x, num[e4].y, num[e4].z, num[e4].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          vals[4 * e4 + e] = p.gate ? apply_gate<T>(f[e], static_cast<const T*>(p.gate)[oi + 4 * e4 + e])
+                                    : MmaOp<T>::from_float(f[e]);
+      }
+      if constexpr (VPL == 4)
+        *reinterpret_cast<uint2*>(out + oi) = *reinterpret_cast<const uint2*>(vals);
+      else
+        *reinterpret_cast<uint4*>(out + oi) = *reinterpret_cast<const uint4*>(vals);
+    } else {
+      float4* dst = reinterpret_cast<float4*>(p.part_o + (hq_idx * p.max_splits + split) * HD + lane * VPL);
+#pragma unroll
+      for (int e4 = 0; e4 < NV; ++e4) dst[e4] = num[e4];
+      if (lane == 0)
+        p.part_lse[hq_idx * p.max_splits + split] = den > 0.f ? M * kLn2 + __logf(den) : -INFINITY;
     }
   }
   MSGL_TRD(7, clock64());      // partial (or final rows) written
@@ -477,11 +507,24 @@ __global__ void __launch_bounds__(NWARPS * 32)
   __threadfence();
   // a warp per query head, a lane per 4 (8) output columns; the splits' rows come straight from
   // scratch (L2), four splits in flight per lane
-  constexpr int VPL = HD / 32, NV = VPL / 4;
+  constexpr int SIF = HD == 256 ? 8 : 16;   // splits in flight per lane
   for (int g = warp; g < G; g += NWARPS) {
     const int64_t hq_idx = static_cast<int64_t>(b) * p.hq + static_cast<int64_t>(h) * G + g;
     const float* lse = p.part_lse + hq_idx * p.max_splits;
     const float* po = p.part_o + hq_idx * p.max_splits * HD + lane * VPL;
+    float ls[SIF];
+    float4 x[SIF][NV];
+    auto load_splits = [&](int s0) {
+#pragma unroll
+      for (int u = 0; u < SIF; ++u) {
+        const int sp = min(s0 + u, splits - 1);
+        ls[u] = __ldcg(lse + sp);
+#pragma unroll
+        for (int e4 = 0; e4 < NV; ++e4)
+          x[u][e4] = __ldcg(reinterpret_cast<const float4*>(po + static_cast<int64_t>(sp) * HD) + e4);
+      }
+    };
+    load_splits(0);   // in flight while the largest log-sum-exp is found
     float M = -INFINITY;
     for (int s = lane; s < splits; s += 32) M = fmaxf(M, __ldcg(lse + s));
 #pragma unroll
@@ -491,19 +534,10 @@ __global__ void __launch_bounds__(NWARPS * 32)
     for (int e = 0; e < VPL; ++e) num[e] = 0.f;
     float den = 0.f;
     if (M != -INFINITY) {
-      for (int s0 = 0; s0 < splits; s0 += 4) {
-        float ls[4];
-        float4 x[4][NV];
+      for (int s0 = 0; s0 < splits; s0 += SIF) {
+        if (s0 > 0) load_splits(s0);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int sp = min(s0 + u, splits - 1);
-          ls[u] = __ldcg(lse + sp);
-#pragma unroll
-          for (int e4 = 0; e4 < NV; ++e4)
-            x[u][e4] = __ldcg(reinterpret_cast<const float4*>(po + static_cast<int64_t>(sp) * HD) + e4);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < SIF; ++u) {
           if (s0 + u >= splits) break;
           const float w = __expf(ls[u] - M);
           den += w;
